@@ -5,4 +5,4 @@ timeout 600 python tests/gpu_kernel_check.py --only "linear,mlp,accum,norm,eleme
 grep -E "SUMMARY|\"ok\": false" gpurun_out/kc6.log | cut -c1-400
 grep -E "linear_fwd speed|mlp fused|attention speed|accumulating" gpurun_out/kc6.log | cut -c1-500
 timeout 600 python bench.py --steps 8 --warmup 3 > gpurun_out/bench_r6.log 2>&1; echo "bench rc=$?"; tail -n 1 gpurun_out/bench_r6.log | cut -c1-1500
-timeout 600 ncu --set full --clock-control none --import-source on -k regex:attn_bwd_kernel -s 2 -c 1 -o gpurun_out/prof_attn_bwd python tests/gpu_kernel_check.py --only "attention speed" --out gpurun_out/tmp.json > gpurun_out/ncu_attn_bwd.log 2>&1; echo "ncu attn bwd rc=$?"
+timeout 600 ncu --set full --clock-control none -k regex:attn_bwd_kernel -s 2 -c 1 -o gpurun_out/prof_attn_bwd python tests/gpu_kernel_check.py --only "attention speed" --out gpurun_out/tmp.json > gpurun_out/ncu_attn_bwd.log 2>&1; echo "ncu attn bwd rc=$?"

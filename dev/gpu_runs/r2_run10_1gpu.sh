@@ -2,7 +2,7 @@
 set -x
 mkdir -p gpurun_out
 for mode in 1 0; do
-LIBAI_B200_GEMM_2CTA=$mode timeout 600 ncu --set full --clock-control none --import-source on -k regex:gemm_kernel -s 2 -c 1 \
+LIBAI_B200_GEMM_2CTA=$mode timeout 600 ncu --set full --clock-control none -k regex:gemm_kernel -s 2 -c 1 \
     -o gpurun_out/r2_ncu_gemm_8192_2cta$mode -f python dev/ncu_gemm.py 8192 8192 8192 0 > gpurun_out/r2_ncu_gemm_2cta$mode.log 2>&1
 tail -2 gpurun_out/r2_ncu_gemm_2cta$mode.log
 ncu -i gpurun_out/r2_ncu_gemm_8192_2cta$mode.ncu-rep --page raw --csv 2>/dev/null | python -c "

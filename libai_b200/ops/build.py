@@ -4,7 +4,7 @@
 
 CUDA sources are compiled for sm_100a only (``-gencode arch=compute_100a,code=sm_100a -lineinfo``);
 nvcc cross-compiles without a GPU.  Objects are cached under ``libai_b200/csrc/build`` keyed by
-source mtime.  ``--sass`` additionally dumps ``cuobjdump -sass`` listings into ``profiles/sass``.
+source mtime.
 """
 from __future__ import annotations
 
@@ -47,7 +47,7 @@ def _stale(src, obj, deps=()):
     return any(os.path.getmtime(p) > t for p in (src,) + tuple(deps) if os.path.exists(p))
 
 
-def build(force: bool = False, verbose: bool = False, sass: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False) -> str:
     import torch
     from torch.utils import cpp_extension
 
@@ -85,44 +85,12 @@ def build(force: bool = False, verbose: bool = False, sass: bool = False) -> str
         _run(["g++", "-shared", "-o", SO_PATH, *objs, f"-L{tlib}", "-lc10", "-ltorch_cpu", "-ltorch", "-lc10_cuda",
               "-ltorch_cuda", f"-L{os.path.join(CUDA_HOME, 'lib64')}", "-lcudart",
               f"-Wl,-rpath,{tlib}", f"-Wl,-rpath,{os.path.join(CUDA_HOME, 'lib64')}"], verbose)
-    if sass:
-        dump_sass()
     return SO_PATH
-
-
-def dump_sass():
-    """Write SASS listings + a mnemonic summary (UTC*MMA / LDTM / UTMALDG ...) to profiles/sass."""
-    out_dir = os.path.join(os.path.dirname(ROOT), "profiles", "sass")
-    os.makedirs(out_dir, exist_ok=True)
-    summary = []
-    for s in CU_SOURCES:
-        obj = os.path.join(BUILD, s + ".o")
-        if not os.path.exists(obj):
-            continue
-        text = subprocess.run([os.path.join(CUDA_HOME, "bin", "cuobjdump"), "-sass", obj], stdout=subprocess.PIPE,
-                              text=True).stdout
-        counts = {}
-        # UTCHMMA / UTCQMMA = tcgen05.mma (bf16 / fp8), .2CTA = cta_group::2 pairs; LDTM/STTM = tcgen05.ld/st; UTMALDG /
-        # UTMASTG / UTMAREDG / UBLKCP = TMA tensor + bulk copies and reductions; LDGMC = multimem.ld_reduce (NVLS in-switch
-        # reduction; multimem.st is a STG.*.STRONG.SYS on a multicast address); USETMAXREG = setmaxnreg
-        for key in ("UTCHMMA", "UTCHMMA.2CTA", "UTCQMMA", "UTCBAR", "LDTM", "STTM", "UTMALDG", "UTMALDG.2D.2CTA", "UTMASTG",
-                    "UTMAREDG", "UBLKCP", "SYNCS", "LDGMC", "USETMAXREG", "RED.E", "REDG", "LDG.E", "STG.E"):
-            counts[key] = text.count(key)
-        summary.append((s, counts))
-        keep = [ln for ln in text.splitlines() if "Function :" in ln or any(k in ln for k in ("UTC", "LDTM", "STTM", "UTMA", "UBLKCP", "LDGMC", "USETMAXREG"))]
-        with open(os.path.join(out_dir, s + ".sass.txt"), "w") as f:
-            f.write("\n".join(keep) + "\n")
-    with open(os.path.join(out_dir, "SUMMARY.md"), "w") as f:
-        f.write("# SASS mnemonic counts per translation unit (cuobjdump -sass, sm_100a)\n\n")
-        for s, c in summary:
-            f.write(f"* `{s}`: " + ", ".join(f"{k}={v}" for k, v in c.items() if v) + "\n")
-    return summary
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
-    ap.add_argument("--sass", action="store_true")
     a = ap.parse_args()
-    print(build(a.force, a.verbose, a.sass))
+    print(build(a.force, a.verbose))
