@@ -1,0 +1,549 @@
+// Sequence-mixer kernels for ragged batches with per-sequence state: zero-centred RMS norms on an fp32 residual stream,
+// short causal convolutions with carried tails, the gated delta rule (one decay per head or per key channel) with its
+// fp32 state, and sliding-window attention over cached low-rank latents (expanded keys/values for prompts, the
+// absorbed form for single-token steps).
+//
+// Conventions.  A step carries B sequences; sequence b brings n_b = seq_off[b+1]-seq_off[b] new tokens that sit
+// packed (no padding) at rows seq_off[b]..seq_off[b+1]-1 of every activation matrix, has past[b] tokens already
+// folded into the state that lives in slot slots[b], and starts from an all-zero state when past[b] == 0 (the slot's
+// old contents are then never read, so a slot can be reused without clearing it).  Activations are `T` (float or
+// bf16, `dtype` 0 / 1); everything that enters a norm, a softmax or a recurrence is converted to fp32 first and the
+// arithmetic is fp32.  This file is built WITHOUT fast-math: the fp32 mode is meant to be exact to rounding.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+  return v;
+}
+// sum over the block (blockDim.x a multiple of 32, at most 1024); every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// ------------------------------------------------------------------------------------------------------------------
+// RMS norm: y = x / sqrt(mean(x^2) + eps) * (offset + w).  One block per row.  Optional gather of the row through
+// `ids` (token embedding + norm in one pass).
+// ------------------------------------------------------------------------------------------------------------------
+template <typename Tin, typename Tw, typename Tout>
+__global__ void rmsnorm_kernel(const Tin* __restrict__ x, long ldx, const int64_t* __restrict__ ids, const Tw* __restrict__ w,
+                               float offset, float eps, Tout* __restrict__ y, long ldy, int n) {
+  __shared__ float red[32];
+  const long row = blockIdx.x;
+  const Tin* xr = x + (ids ? (long)ids[row] : row) * ldx;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) { float v = ldf(xr + i); ss += v * v; }
+  ss = block_sum(ss, red);
+  const float r = 1.f / sqrtf(ss / (float)n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) stf(y + row * ldy + i, ldf(xr + i) * r * (offset + ldf(w + i)));
+}
+
+// out[row, 0:n] = act(in[row, 0:n]) on column slices; act 0: copy, 1: relu(x)^2, 2: silu, 3: gelu_tanh
+template <typename Tin, typename Tout>
+__global__ void slice_act_kernel(const Tin* __restrict__ in, long ldi, Tout* __restrict__ out, long ldo, long rows, int n, int act) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * n) return;
+  const long r = idx / n; const int c = (int)(idx - r * n);
+  float v = ldf(in + r * ldi + c);
+  if (act == 1) { v = fmaxf(v, 0.f); v = v * v; }
+  else if (act == 2) v = v * sigmoidf_(v);
+  else if (act == 3) v = 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+  stf(out + r * ldo + c, v);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Short causal convolution per channel + SiLU.  in: [tokens, ldi] (C channels from column 0), w: [C, taps] with the
+// last tap on the current token, tail: [slots, taps-1, C] = the last taps-1 inputs of every sequence.
+// ------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void short_conv_kernel(const T* __restrict__ in, long ldi, const T* __restrict__ w, const T* __restrict__ tail,
+                                  const int* __restrict__ tok_seq, const int* __restrict__ seq_off, const int* __restrict__ slots,
+                                  const int* __restrict__ past, T* __restrict__ out, long ldo, long tokens, int C, int taps) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= tokens * C) return;
+  const long tok = idx / C; const int c = (int)(idx - tok * C);
+  const int b = tok_seq[tok];
+  const int t = (int)(tok - seq_off[b]);
+  const bool has_past = past[b] > 0;
+  const T* tl = tail + (long)slots[b] * (taps - 1) * C;
+  float acc = 0.f;
+  for (int k = 0; k < taps; ++k) {
+    const int tp = t - k;
+    float v;
+    if (tp >= 0) v = ldf(in + (tok - k) * ldi + c);
+    else v = has_past ? ldf(tl + (long)(taps - 1 + tp) * C + c) : 0.f;
+    acc += ldf(w + (long)c * taps + (taps - 1 - k)) * v;
+  }
+  stf(out + tok * ldo + c, acc * sigmoidf_(acc));
+}
+
+template <typename T>
+__global__ void conv_tail_kernel(const T* __restrict__ in, long ldi, T* __restrict__ tail, const int* __restrict__ seq_off,
+                                 const int* __restrict__ slots, const int* __restrict__ past, int B, int C, int taps) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long)B * C) return;
+  const int b = (int)(idx / C), c = (int)(idx - (long)b * C);
+  const int n = seq_off[b + 1] - seq_off[b];
+  const bool has_past = past[b] > 0;
+  T* tl = tail + (long)slots[b] * (taps - 1) * C;
+  for (int i = 0; i < taps - 1; ++i) {          // ascending: new[i] only reads old[i + n], never a rewritten entry
+    const int tp = n - (taps - 1) + i;
+    float v;
+    if (tp >= 0) v = ldf(in + ((long)seq_off[b] + tp) * ldi + c);
+    else v = (has_past && i + n < taps - 1) ? ldf(tl + (long)(i + n) * C + c) : 0.f;
+    stf(tl + (long)i * C + c, v);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Gated delta rule.  Per head, with S [D, V] in fp32:   S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;
+// o = S^T q.  q and k arrive after the convolution, are normalised here to unit length per head (eps inside the
+// root) and q is scaled by D^-1/2.  g = exp(-exp(A_log) softplus(a + dt_bias)) per head (chan == 0) or per key channel
+// (chan == 1); beta = sigmoid(b).  Columns of S are independent: a block owns `VT` of them for one (sequence, head),
+// every column is shared by R lanes that each keep DPT rows (rows i = d R + r) in registers, and tokens are staged
+// through shared memory `CT` at a time so that the serial part only touches registers and shared memory.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int CT = 16;
+
+template <typename T, int DPT>
+__global__ void __launch_bounds__(1024)
+delta_scan_kernel(const T* __restrict__ qkv, long ldq, int koff, int voff, const T* __restrict__ a, long lda,
+                  const T* __restrict__ bl, long ldb, const T* __restrict__ A_log, const T* __restrict__ dt_bias,
+                  float* __restrict__ S, const int* __restrict__ seq_off, const int* __restrict__ slots,
+                  const int* __restrict__ past, float* __restrict__ out, int H, int KH, int D, int V, int R, int VT, int chan) {
+  extern __shared__ float sm[];
+  const int b = blockIdx.x / H, h = blockIdx.x % H, kh = h / (H / KH);
+  const int j0 = blockIdx.y * VT;
+  const int Dp = R * DPT;                       // padded row count (rows >= D hold zeros)
+  float* sk = sm;                               // [CT][Dp]
+  float* sq = sk + CT * Dp;                     // [CT][Dp]
+  float* sg = sq + CT * Dp;                     // [CT][chan ? Dp : 1]
+  const int gl = chan ? Dp : 1;
+  float* sv = sg + CT * gl;                     // [CT][VT]
+  float* sbeta = sv + CT * VT;                  // [CT]
+  float* skq = sbeta + CT;                      // [CT]
+  const int tid = threadIdx.x, nth = blockDim.x;
+  const int r = tid % R, jj = tid / R, j = j0 + jj;
+  const bool col_ok = jj < VT && j < V;
+  const int n = seq_off[b + 1] - seq_off[b];
+  const long tok0 = seq_off[b];
+  float* Sg = S + ((long)slots[b] * H + h) * (long)D * V;
+  float s[DPT];
+#pragma unroll
+  for (int d = 0; d < DPT; ++d) {
+    const int i = d * R + r;
+    s[d] = (past[b] > 0 && col_ok && i < D) ? Sg[(long)i * V + j] : 0.f;
+  }
+  const float decay_rate = chan ? 0.f : expf(ldf(A_log + h));
+  const float rate_c = expf(ldf(A_log + h));
+  const float qs = 1.f / sqrtf((float)D);
+  for (int c0 = 0; c0 < n; c0 += CT) {
+    const int ct = min(CT, n - c0);
+    __syncthreads();
+    for (int e = tid; e < ct * Dp; e += nth) {
+      const int t = e / Dp, i = e - t * Dp;
+      const long row = tok0 + c0 + t;
+      float kv = 0.f, qv = 0.f, gv = 1.f;
+      if (i < D) {
+        qv = ldf(qkv + row * ldq + kh * D + i);
+        kv = ldf(qkv + row * ldq + koff + kh * D + i);
+        if (chan) gv = expf(-rate_c * softplusf_(ldf(a + row * lda + h * D + i) + ldf(dt_bias + h * D + i)));
+      }
+      sk[e] = kv; sq[e] = qv;
+      if (chan) sg[e] = gv;
+    }
+    for (int e = tid; e < ct * VT; e += nth) {
+      const int t = e / VT, c = e - t * VT;
+      sv[e] = (j0 + c < V) ? ldf(qkv + (tok0 + c0 + t) * ldq + voff + h * V + j0 + c) : 0.f;
+    }
+    for (int t = tid; t < ct; t += nth) {
+      const long row = tok0 + c0 + t;
+      sbeta[t] = sigmoidf_(ldf(bl + row * ldb + h));
+      if (!chan) sg[t] = expf(-decay_rate * softplusf_(ldf(a + row * lda + h) + ldf(dt_bias + h)));
+    }
+    __syncthreads();
+    // unit length per token: one warp per token
+    for (int t = tid >> 5; t < ct; t += nth >> 5) {
+      float kk = 0.f, qq = 0.f;
+      for (int i = tid & 31; i < Dp; i += 32) { kk += sk[t * Dp + i] * sk[t * Dp + i]; qq += sq[t * Dp + i] * sq[t * Dp + i]; }
+      kk = warp_sum(kk); qq = warp_sum(qq);
+      const float ksc = 1.f / sqrtf(kk + 1e-6f), qsc = qs / sqrtf(qq + 1e-6f);
+      float kq = 0.f;
+      for (int i = tid & 31; i < Dp; i += 32) {
+        const float kx = sk[t * Dp + i] * ksc, qx = sq[t * Dp + i] * qsc;
+        sk[t * Dp + i] = kx; sq[t * Dp + i] = qx; kq += kx * qx;
+      }
+      kq = warp_sum(kq);
+      if ((tid & 31) == 0) skq[t] = kq;
+    }
+    __syncthreads();
+    // every thread walks the tokens (lanes of idle columns included: the shuffles below name the whole warp)
+    for (int t = 0; t < ct; ++t) {
+      float pk = 0.f, pq = 0.f;
+      const float* kt = sk + t * Dp; const float* qt = sq + t * Dp; const float* gt = sg + t * gl;
+#pragma unroll
+      for (int d = 0; d < DPT; ++d) {
+        const int i = d * R + r;
+        s[d] *= chan ? gt[i] : gt[0];
+        pk += s[d] * kt[i]; pq += s[d] * qt[i];
+      }
+      for (int m = R >> 1; m > 0; m >>= 1) { pk += __shfl_xor_sync(0xffffffffu, pk, m); pq += __shfl_xor_sync(0xffffffffu, pq, m); }
+      const float u = sbeta[t] * ((jj < VT ? sv[t * VT + jj] : 0.f) - pk);
+#pragma unroll
+      for (int d = 0; d < DPT; ++d) s[d] += kt[d * R + r] * u;
+      if (r == 0 && col_ok) out[(tok0 + c0 + t) * (long)(H * V) + h * V + j] = pq + skq[t] * u;
+    }
+  }
+  if (col_ok) {
+#pragma unroll
+    for (int d = 0; d < DPT; ++d) { const int i = d * R + r; if (i < D) Sg[(long)i * V + j] = s[d]; }
+  }
+}
+
+// y[tok, h, :] = o / rms(o over V) * w * act(gate[tok, h, :]);  act 0: silu, 1: sigmoid.  One warp per (token, head).
+template <typename T>
+__global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const T* __restrict__ gate, long ldg, const T* __restrict__ w,
+                                     float eps, int act, T* __restrict__ y, long ldy, long rows, int H, int V) {
+  const long wid = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= rows * H) return;
+  const long tok = wid / H; const int h = (int)(wid - tok * H);
+  const float* orow = o + (tok * H + h) * (long)V;
+  float ss = 0.f;
+  for (int i = lane; i < V; i += 32) ss += orow[i] * orow[i];
+  ss = warp_sum(ss);
+  const float rr = 1.f / sqrtf(ss / (float)V + eps);
+  for (int i = lane; i < V; i += 32) {
+    const float g = ldf(gate + tok * ldg + h * V + i);
+    const float ga = act == 0 ? g * sigmoidf_(g) : sigmoidf_(g);
+    stf(y + tok * ldy + h * V + i, orow[i] * rr * ldf(w + i) * ga);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Latent cache: ring[slot][p % ring_len] holds the latent of position p; ring_len >= window.  `gather` lays out, for every
+// sequence, the still-visible cached latents followed by the step's new ones (ext rows); `write` stores the new ones.
+// ------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void latent_gather_kernel(const T* __restrict__ ring, const T* __restrict__ cnew, const int* __restrict__ ext_seq,
+                                     const int* __restrict__ ext_off, const int* __restrict__ seq_off, const int* __restrict__ slots,
+                                     const int* __restrict__ past, T* __restrict__ ext, long rows, int C, int ring_len) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * C) return;
+  const long e = idx / C; const int c = (int)(idx - e * C);
+  const int b = ext_seq[e];
+  const int ie = (int)(e - ext_off[b]);
+  const int n = seq_off[b + 1] - seq_off[b];
+  const int npast = ext_off[b + 1] - ext_off[b] - n;
+  if (ie < npast) {
+    const int pos = past[b] - npast + ie;
+    ext[idx] = ring[((long)slots[b] * ring_len + pos % ring_len) * C + c];
+  } else {
+    ext[idx] = cnew[((long)seq_off[b] + ie - npast) * C + c];
+  }
+}
+
+template <typename T>
+__global__ void latent_write_kernel(T* __restrict__ ring, const T* __restrict__ cnew, const int* __restrict__ tok_seq,
+                                    const int* __restrict__ seq_off, const int* __restrict__ slots, const int* __restrict__ past,
+                                    long tokens, int C, int ring_len) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= tokens * C) return;
+  const long tok = idx / C; const int c = (int)(idx - tok * C);
+  const int b = tok_seq[tok];
+  const int t = (int)(tok - seq_off[b]), n = seq_off[b + 1] - seq_off[b];
+  if (t < n - ring_len) return;                 // an older token of this step would be overwritten anyway
+  const int pos = past[b] + t;
+  ring[((long)slots[b] * ring_len + pos % ring_len) * C + c] = cnew[idx];
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Sliding-window attention on expanded keys / values.  q: [tokens, H*D]; kv: [ext rows, H*D + H*V] (keys, then values);
+// query t of sequence b sits at ext row ext_off[b] + npast + t and sees the `window` ext rows ending at its own, never
+// crossing the start of its sequence's ext range.  One warp per (token, head): lanes take keys for the scores and value
+// channels for the output; softmax in fp32, streamed 32 keys at a time.  The head's output is multiplied by
+// sigmoid(gate[tok, h]) when a gate is given.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int ATT_MAXV = 8;    // value channels per lane: V <= 256
+
+template <typename T>
+__global__ void window_attention_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ kv, long ldkv, const T* __restrict__ gate,
+                                        long ldg, const int* __restrict__ tok_seq, const int* __restrict__ seq_off,
+                                        const int* __restrict__ ext_off, T* __restrict__ y, long ldy, long tokens, int H, int D,
+                                        int V, int window, float scale) {
+  extern __shared__ float sm[];
+  const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long wid = (long)blockIdx.x * (blockDim.x >> 5) + wib;
+  if (wid >= tokens * H) return;                 // no block-level sync below
+  const long tok = wid / H; const int h = (int)(wid - tok * H);
+  const int b = tok_seq[tok];
+  const int n = seq_off[b + 1] - seq_off[b];
+  const int npast = ext_off[b + 1] - ext_off[b] - n;
+  const long eq = (long)ext_off[b] + npast + (tok - seq_off[b]);
+  long e0 = eq - window + 1;
+  if (e0 < ext_off[b]) e0 = ext_off[b];
+  float* qs = sm + wib * D;
+  for (int i = lane; i < D; i += 32) qs[i] = ldf(q + tok * ldq + h * D + i) * scale;
+  __syncwarp();
+  float m = -INFINITY, l = 0.f, acc[ATT_MAXV];
+#pragma unroll
+  for (int i = 0; i < ATT_MAXV; ++i) acc[i] = 0.f;
+  for (long e = e0; e <= eq; e += 32) {
+    const long mine = e + lane;
+    float sc = -INFINITY;
+    if (mine <= eq) {
+      const T* kr = kv + mine * ldkv + h * D;
+      float d = 0.f;
+      for (int i = 0; i < D; ++i) d += qs[i] * ldf(kr + i);
+      sc = d;
+    }
+    const float mn = fmaxf(m, warp_max(sc));
+    const float corr = expf(m - mn);             // m = -inf on the first block: exp(-inf) = 0
+    const float p = mine <= eq ? expf(sc - mn) : 0.f;
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int i = 0; i < ATT_MAXV; ++i) acc[i] *= corr;
+    const int cnt = (int)min((long)32, eq - e + 1);
+    for (int k = 0; k < cnt; ++k) {
+      const float pk = __shfl_sync(0xffffffffu, p, k);
+      const T* vr = kv + (e + k) * ldkv + (long)H * D + h * V;
+#pragma unroll
+      for (int i = 0; i < ATT_MAXV; ++i) { const int c = lane + 32 * i; if (c < V) acc[i] += pk * ldf(vr + c); }
+    }
+    m = mn;
+  }
+  const float g = gate ? sigmoidf_(ldf(gate + tok * ldg + h)) : 1.f;
+  const float inv = g / l;
+#pragma unroll
+  for (int i = 0; i < ATT_MAXV; ++i) { const int c = lane + 32 * i; if (c < V) stf(y + tok * ldy + h * V + c, acc[i] * inv); }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Single-token steps in the absorbed form: the query already carries the key up-projection (qa [B, H, C], fp32), so the
+// scores and the weighted sum run on the cached latents themselves; the new token's latent (cnew [B, C]) is position
+// past[b], the others come from the ring.  out: [B, H, C] fp32 = softmax-weighted latent per head (the value
+// up-projection follows as a batched matrix product).  One warp per (sequence, head).
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int ABS_MAXC = 32;   // latent channels per lane: C <= 1024
+
+template <typename T>
+__global__ void latent_decode_kernel(const float* __restrict__ qa, const T* __restrict__ ring, const T* __restrict__ cnew,
+                                     const int* __restrict__ slots, const int* __restrict__ past, float* __restrict__ out, int B, int H,
+                                     int C, int ring_len, int window, float scale) {
+  extern __shared__ float sm[];
+  const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long wid = (long)blockIdx.x * (blockDim.x >> 5) + wib;
+  if (wid >= (long)B * H) return;
+  const int b = (int)(wid / H), h = (int)(wid - (long)b * H);
+  const int p = past[b];
+  int p0 = p - window + 1; if (p0 < 0) p0 = 0;
+  float* qs = sm + wib * C;
+  for (int i = lane; i < C; i += 32) qs[i] = qa[((long)b * H + h) * C + i] * scale;
+  __syncwarp();
+  const T* rb = ring + (long)slots[b] * ring_len * C;
+  float m = -INFINITY, l = 0.f, acc[ABS_MAXC];
+#pragma unroll
+  for (int i = 0; i < ABS_MAXC; ++i) acc[i] = 0.f;
+  for (int e = p0; e <= p; e += 32) {
+    const int mine = e + lane;
+    float sc = -INFINITY;
+    if (mine <= p) {
+      const T* cr = mine == p ? cnew + (long)b * C : rb + (long)(mine % ring_len) * C;
+      float d = 0.f;
+      for (int i = 0; i < C; ++i) d += qs[i] * ldf(cr + i);
+      sc = d;
+    }
+    const float mn = fmaxf(m, warp_max(sc));
+    const float corr = expf(m - mn);
+    const float pr = mine <= p ? expf(sc - mn) : 0.f;
+    l = l * corr + warp_sum(pr);
+#pragma unroll
+    for (int i = 0; i < ABS_MAXC; ++i) acc[i] *= corr;
+    const int cnt = min(32, p - e + 1);
+    for (int k = 0; k < cnt; ++k) {
+      const float pk = __shfl_sync(0xffffffffu, pr, k);
+      const T* cr = (e + k) == p ? cnew + (long)b * C : rb + (long)((e + k) % ring_len) * C;
+#pragma unroll
+      for (int i = 0; i < ABS_MAXC; ++i) { const int c = lane + 32 * i; if (c < C) acc[i] += pk * ldf(cr + c); }
+    }
+    m = mn;
+  }
+  const float inv = 1.f / l;
+#pragma unroll
+  for (int i = 0; i < ABS_MAXC; ++i) { const int c = lane + 32 * i; if (c < C) out[((long)b * H + h) * C + c] = acc[i] * inv; }
+}
+
+// y[b, h*V + v] = x[b, h, v] * sigmoid(gate[b, h]) (fp32 in, T out)
+template <typename T>
+__global__ void head_gate_kernel(const float* __restrict__ x, const T* __restrict__ gate, long ldg, T* __restrict__ y, long ldy,
+                                 long rows, int H, int V) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * H * V) return;
+  const long row = idx / ((long)H * V); const int hv = (int)(idx - row * (long)H * V); const int h = hv / V;
+  const float g = gate ? sigmoidf_(ldf(gate + row * ldg + h)) : 1.f;
+  stf(y + row * ldy + hv, x[idx] * g);
+}
+
+inline int cdiv(long a, long b) { return (int)((a + b - 1) / b); }
+inline int ok() { return (int)cudaGetLastError(); }
+typedef __nv_bfloat16 bf16;
+
+}  // namespace
+
+#define DISPATCH(dtype, ...)                         \
+  if ((dtype) == 0) { typedef float T; __VA_ARGS__; } \
+  else { typedef bf16 T; __VA_ARGS__; }
+
+extern "C" {
+
+// x: rows of `xdtype` (0 fp32, 1 bf16); w and y: `dtype`; ids optional row gather
+int lbs_rmsnorm(const void* x, long ldx, int xdtype, const int64_t* ids, const void* w, float offset, float eps, void* y, long ldy,
+                int ydtype, int wdtype, long rows, int n, cudaStream_t s) {
+  if (rows == 0) return 0;
+  const int th = n >= 1024 ? 256 : (n >= 256 ? 128 : 64);
+#define RN(TI, TW, TO) rmsnorm_kernel<TI, TW, TO><<<(unsigned)rows, th, 0, s>>>((const TI*)x, ldx, ids, (const TW*)w, offset, eps, (TO*)y, ldy, n)
+  const int key = xdtype * 4 + wdtype * 2 + ydtype;
+  switch (key) {
+    case 0: RN(float, float, float); break;
+    case 1: RN(float, float, bf16); break;
+    case 2: RN(float, bf16, float); break;
+    case 3: RN(float, bf16, bf16); break;
+    case 4: RN(bf16, float, float); break;
+    case 5: RN(bf16, float, bf16); break;
+    case 6: RN(bf16, bf16, float); break;
+    default: RN(bf16, bf16, bf16); break;
+  }
+#undef RN
+  return ok();
+}
+
+int lbs_slice_act(const void* in, long ldi, int idtype, void* out, long ldo, int odtype, long rows, int n, int act, cudaStream_t s) {
+  if (rows * n == 0) return 0;
+  const int g = cdiv(rows * n, 256);
+  if (idtype == 0 && odtype == 0) slice_act_kernel<float, float><<<g, 256, 0, s>>>((const float*)in, ldi, (float*)out, ldo, rows, n, act);
+  else if (idtype == 0) slice_act_kernel<float, bf16><<<g, 256, 0, s>>>((const float*)in, ldi, (bf16*)out, ldo, rows, n, act);
+  else if (odtype == 0) slice_act_kernel<bf16, float><<<g, 256, 0, s>>>((const bf16*)in, ldi, (float*)out, ldo, rows, n, act);
+  else slice_act_kernel<bf16, bf16><<<g, 256, 0, s>>>((const bf16*)in, ldi, (bf16*)out, ldo, rows, n, act);
+  return ok();
+}
+
+int lbs_short_conv(const void* in, long ldi, const void* w, void* tail, const int* tok_seq, const int* seq_off, const int* slots,
+                   const int* past, void* out, long ldo, long tokens, int B, int C, int taps, int dtype, cudaStream_t s) {
+  if (tokens == 0) return 0;
+  DISPATCH(dtype, {
+    short_conv_kernel<T><<<cdiv(tokens * C, 256), 256, 0, s>>>((const T*)in, ldi, (const T*)w, (const T*)tail, tok_seq, seq_off, slots,
+                                                                past, (T*)out, ldo, tokens, C, taps);
+    if (taps > 1)
+      conv_tail_kernel<T><<<cdiv((long)B * C, 256), 256, 0, s>>>((const T*)in, ldi, (T*)tail, seq_off, slots, past, B, C, taps);
+  });
+  return ok();
+}
+
+int lbs_delta_scan(const void* qkv, long ldq, int koff, int voff, const void* a, long lda, const void* bl, long ldb, const void* A_log,
+                   const void* dt_bias, float* S, const int* seq_off, const int* slots, const int* past, float* out, int B, int H,
+                   int KH, int D, int V, int chan, int dtype, cudaStream_t s) {
+  if (B == 0) return 0;
+  if (D > 256 || H % KH != 0) return -1;
+  const int dpt = D <= 128 ? 4 : 8;
+  int R = 1;
+  while (R * dpt < D) R <<= 1;                   // lanes per column, a power of two <= 32
+  int VT = V < 1024 / R ? V : 1024 / R;          // columns per block
+  if (VT > 64) VT = 64;                          // more blocks per head: columns are independent
+  int threads = ((VT * R + 31) / 32) * 32;
+  const int Dp = R * dpt;
+  const size_t smem = sizeof(float) * ((size_t)CT * Dp * 2 + (size_t)CT * (chan ? Dp : 1) + (size_t)CT * VT + 2 * CT);
+  dim3 grid((unsigned)(B * H), (unsigned)((V + VT - 1) / VT));
+#define DS(TT, P)                                                                                                              \
+  {                                                                                                                            \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<TT, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    delta_scan_kernel<TT, P><<<grid, threads, smem, s>>>((const TT*)qkv, ldq, koff, voff, (const TT*)a, lda, (const TT*)bl, ldb,   \
+                                                        (const TT*)A_log, (const TT*)dt_bias, S, seq_off, slots, past, out, H, KH, \
+                                                        D, V, R, VT, chan);                                                      \
+  }
+  if (dtype == 0) { if (dpt == 4) DS(float, 4) else DS(float, 8) }
+  else { if (dpt == 4) DS(bf16, 4) else DS(bf16, 8) }
+#undef DS
+  return ok();
+}
+
+int lbs_gated_rmsnorm(const float* o, const void* gate, long ldg, const void* w, float eps, int act, void* y, long ldy, long rows,
+                      int H, int V, int dtype, cudaStream_t s) {
+  if (rows == 0) return 0;
+  DISPATCH(dtype, gated_rmsnorm_kernel<T><<<cdiv(rows * H * 32, 256), 256, 0, s>>>(o, (const T*)gate, ldg, (const T*)w, eps, act,
+                                                                                    (T*)y, ldy, rows, H, V));
+  return ok();
+}
+
+int lbs_latent_gather(const void* ring, const void* cnew, const int* ext_seq, const int* ext_off, const int* seq_off, const int* slots,
+                      const int* past, void* ext, long rows, int C, int ring_len, int dtype, cudaStream_t s) {
+  if (rows == 0) return 0;
+  DISPATCH(dtype, latent_gather_kernel<T><<<cdiv(rows * C, 256), 256, 0, s>>>((const T*)ring, (const T*)cnew, ext_seq, ext_off, seq_off,
+                                                                               slots, past, (T*)ext, rows, C, ring_len));
+  return ok();
+}
+
+int lbs_latent_write(void* ring, const void* cnew, const int* tok_seq, const int* seq_off, const int* slots, const int* past,
+                     long tokens, int C, int ring_len, int dtype, cudaStream_t s) {
+  if (tokens == 0) return 0;
+  DISPATCH(dtype, latent_write_kernel<T><<<cdiv(tokens * C, 256), 256, 0, s>>>((T*)ring, (const T*)cnew, tok_seq, seq_off, slots, past,
+                                                                                tokens, C, ring_len));
+  return ok();
+}
+
+int lbs_window_attention(const void* q, long ldq, const void* kv, long ldkv, const void* gate, long ldg, const int* tok_seq,
+                         const int* seq_off, const int* ext_off, void* y, long ldy, long tokens, int H, int D, int V, int window,
+                         float scale, int dtype, cudaStream_t s) {
+  if (tokens == 0) return 0;
+  if (V > 32 * ATT_MAXV) return -1;
+  const int warps = 4;
+  const size_t smem = sizeof(float) * warps * D;
+  DISPATCH(dtype, window_attention_kernel<T><<<cdiv(tokens * H, warps), warps * 32, smem, s>>>(
+                      (const T*)q, ldq, (const T*)kv, ldkv, (const T*)gate, ldg, tok_seq, seq_off, ext_off, (T*)y, ldy, tokens, H, D, V,
+                      window, scale));
+  return ok();
+}
+
+int lbs_latent_decode(const float* qa, const void* ring, const void* cnew, const int* slots, const int* past, float* out, int B, int H,
+                      int C, int ring_len, int window, float scale, int dtype, cudaStream_t s) {
+  if (B == 0) return 0;
+  if (C > 32 * ABS_MAXC) return -1;
+  const int warps = 4;
+  const size_t smem = sizeof(float) * warps * C;
+  DISPATCH(dtype, latent_decode_kernel<T><<<cdiv((long)B * H, warps), warps * 32, smem, s>>>(qa, (const T*)ring, (const T*)cnew, slots,
+                                                                                              past, out, B, H, C, ring_len, window, scale));
+  return ok();
+}
+
+int lbs_head_gate(const float* x, const void* gate, long ldg, void* y, long ldy, long rows, int H, int V, int dtype, cudaStream_t s) {
+  if (rows == 0) return 0;
+  DISPATCH(dtype, head_gate_kernel<T><<<cdiv(rows * H * V, 256), 256, 0, s>>>(x, (const T*)gate, ldg, (T*)y, ldy, rows, H, V));
+  return ok();
+}
+
+}  // extern "C"

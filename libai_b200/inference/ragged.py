@@ -1,0 +1,56 @@
+"""Ragged step descriptor: which sequences a step carries, how many new tokens each brings, where their state lives.
+
+The generation path of the stateful models works on packed rows (no padding): sequence ``b`` owns rows
+``offsets[b] … offsets[b] + lens[b] - 1`` of every activation matrix of the step, its state sits in slot ``slots[b]`` of the
+:class:`~libai_b200.inference.state_cache.SequenceStateCache` and already covers ``past[b]`` tokens.  The descriptor is built
+on the host and shipped to the device as ONE int32 tensor; the kernels index it directly.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Sequence
+
+import torch
+
+
+class WindowExt:
+    """Row layout of the keys of a windowed attention step: per sequence the ``npast[b] = min(past[b], window - 1)`` cached
+    positions its first query still sees, then its new tokens."""
+
+    def __init__(self, rb: "RaggedBatch", window: int):
+        self.npast = [min(p, window - 1) for p in rb.past_list]
+        lens = [a + n for a, n in zip(self.npast, rb.lens)]
+        self.offsets = [0]
+        for n in lens:
+            self.offsets.append(self.offsets[-1] + n)
+        self.rows = self.offsets[-1]
+        seq = [b for b, n in enumerate(lens) for _ in range(n)]
+        packed = torch.tensor(self.offsets + seq, dtype=torch.int32).to(rb.device, non_blocking=True)
+        self.ext_off, self.ext_seq = packed[: rb.B + 1], packed[rb.B + 1:]
+
+
+class RaggedBatch:
+    def __init__(self, lens: Sequence[int], slots: Sequence[int], past: Sequence[int], device):
+        assert len(lens) == len(slots) == len(past) and all(n > 0 for n in lens)
+        self.B, self.device = len(lens), torch.device(device)
+        self.lens, self.slot_list, self.past_list = list(lens), list(slots), list(past)
+        self.offsets: List[int] = [0]
+        for n in self.lens:
+            self.offsets.append(self.offsets[-1] + n)
+        self.tokens = self.offsets[-1]
+        self.single = all(n == 1 for n in self.lens)          # every sequence goes on by one token
+        tok_seq = [b for b, n in enumerate(self.lens) for _ in range(n)]
+        packed = torch.tensor(self.offsets + self.slot_list + self.past_list + tok_seq, dtype=torch.int32)
+        packed = packed.to(self.device, non_blocking=True)
+        B = self.B
+        self.seq_off, self.slots, self.past = packed[: B + 1], packed[B + 1: 2 * B + 1], packed[2 * B + 1: 3 * B + 1]
+        self.tok_seq = packed[3 * B + 1:]
+        self._ext: Dict[int, WindowExt] = {}
+
+    def ext(self, window: int) -> WindowExt:
+        if window not in self._ext:
+            self._ext[window] = WindowExt(self, window)
+        return self._ext[window]
+
+    def last_rows(self) -> List[int]:
+        """Packed row of every sequence's last new token."""
+        return [self.offsets[b + 1] - 1 for b in range(self.B)]

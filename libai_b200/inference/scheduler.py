@@ -1,0 +1,103 @@
+"""Request scheduler of the stateful models: requests → slots of the state cache → ragged steps of the model's step function.
+
+A request enters with its first tokens, goes on with whatever tokens later steps bring (one at a time while decoding, or a
+further portion of its prompt) and gives its slot back when it is finished.  All entries of a step run as ONE ragged batch;
+nothing is padded.  :meth:`RequestScheduler.generate` is batched generation on top of it: one step for all prompts, then one
+token per live request per step, requests leaving the batch as they finish; the next token is chosen by the framework's
+logits processors / warpers (greedy when none samples).
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import torch
+
+from libai_b200.inference.generator.generation_logits_processor import (
+    LogitsProcessorList,
+    TemperatureLogitsWarper,
+    TopKLogitsWarper,
+    TopPLogitsWarper,
+)
+from libai_b200.inference.ragged import RaggedBatch
+
+
+class RequestScheduler:
+    def __init__(self, model, max_tokens: Optional[int] = None):
+        self.model = model
+        self.cache = model.state_cache()
+        self.max_tokens = max_tokens
+        self.slot_of: Dict[Hashable, int] = {}
+        self.device = model.head.device
+
+    def live_tokens(self) -> int:
+        return sum(self.cache.length[s] for s in self.slot_of.values())
+
+    def step(self, entries: Sequence[Tuple[Hashable, Sequence[int], Sequence[int]]]):
+        """``entries``: ``(request id, next tokens, positions among them whose logits are wanted)``.  Returns the wanted
+        logits ``[Σ wanted, vocab]`` fp32 in the order of the entries (``None`` when nothing is wanted)."""
+        if not entries:
+            return None
+        new = sum(len(toks) for _, toks, _ in entries)
+        if self.max_tokens is not None and self.live_tokens() + new > self.max_tokens:
+            raise RuntimeError(f"the step would hold {self.live_tokens() + new} tokens; the limit is {self.max_tokens}")
+        for rid, _, _ in entries:
+            if rid not in self.slot_of:
+                self.slot_of[rid] = self.cache.allocate(1)[0]
+        slots = [self.slot_of[rid] for rid, _, _ in entries]
+        lens = [len(toks) for _, toks, _ in entries]
+        rb = RaggedBatch(lens, slots, [self.cache.length[s] for s in slots], self.device)
+        flat = [t for _, toks, _ in entries for t in toks]
+        rows = [rb.offsets[b] + w for b, (_, _, want) in enumerate(entries) for w in want]
+        packed = torch.tensor(flat + rows, dtype=torch.long).to(self.device, non_blocking=True)
+        tokens, row_idx = packed[: len(flat)], packed[len(flat):]
+        logits = self.model.step(tokens, rb, row_idx)
+        return logits if rows else None
+
+    def finish(self, request_ids) -> None:
+        for rid in request_ids:
+            slot = self.slot_of.pop(rid, None)
+            if slot is not None:
+                self.cache.free([slot])
+
+    @torch.no_grad()
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int, eos_token_id: Optional[int] = None,
+                 do_sample: bool = False, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0,
+                 logits_processor: Optional[LogitsProcessorList] = None) -> List[List[int]]:
+        """Prompts of any lengths → the generated continuations (without the prompt, ending with ``eos_token_id`` when it
+        was produced)."""
+        processors = logits_processor if logits_processor is not None else LogitsProcessorList()
+        warpers = LogitsProcessorList()
+        if do_sample:
+            if temperature != 1.0:
+                warpers.append(TemperatureLogitsWarper(float(temperature)))
+            if top_k:
+                warpers.append(TopKLogitsWarper(top_k=int(top_k)))
+            if top_p < 1.0:
+                warpers.append(TopPLogitsWarper(top_p=float(top_p)))
+        ids = [("gen", id(prompts), i) for i in range(len(prompts))]
+        seqs = [list(p) for p in prompts]
+        out: List[List[int]] = [[] for _ in prompts]
+        live = list(range(len(prompts)))
+        entries = [(ids[i], seqs[i], [len(seqs[i]) - 1]) for i in live]
+        try:
+            while live and max_new_tokens > 0:
+                logits = self.step(entries)
+                nxt = []
+                for row, i in enumerate(live):
+                    so_far = torch.tensor([seqs[i]], dtype=torch.long, device=logits.device)
+                    scores = warpers(so_far, processors(so_far, logits[row:row + 1]))
+                    tok = int(torch.multinomial(torch.softmax(scores, -1), 1)) if do_sample else int(scores.argmax(-1))
+                    nxt.append(tok)
+                still = []
+                for i, tok in zip(live, nxt):
+                    seqs[i].append(tok)
+                    out[i].append(tok)
+                    if (eos_token_id is not None and tok == eos_token_id) or len(out[i]) >= max_new_tokens:
+                        self.finish([ids[i]])
+                    else:
+                        still.append(i)
+                live = still
+                entries = [(ids[i], [seqs[i][-1]], [0]) for i in live]
+        finally:
+            self.finish(ids)
+        return out

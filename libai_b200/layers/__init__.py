@@ -15,3 +15,5 @@ __all__ = [
     "Linear", "Linear1D", "Conv1D", "MLP", "LayerNorm", "RMSLayerNorm", "TransformerLayer",
     "MultiheadAttention", "AttnMaskType", "ParallelCrossEntropyLoss", "LMLogits", "DropPath",
 ]
+from .delta_rule import GatedDeltaMixer
+from .latent_attention import LatentAttention

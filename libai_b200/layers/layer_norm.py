@@ -59,20 +59,29 @@ class LayerNorm(nn.Module):
 
 
 class RMSLayerNorm(nn.Module):
-    """T5 / Llama style RMS norm: ``x * rsqrt(mean(x²) + eps) * weight`` (no mean subtraction, no bias)."""
+    """T5 / Llama style RMS norm: ``x * rsqrt(mean(x²) + eps) * weight`` (no mean subtraction, no bias).
+    ``zero_centered``: the stored weight is the deviation from one — ``x * rsqrt(mean(x²) + eps) * (1 + weight)``."""
 
-    def __init__(self, normalized_shape, eps=1e-6, *, layer_idx=0, dtype=None):
+    def __init__(self, normalized_shape, eps=1e-6, *, layer_idx=0, dtype=None, zero_centered=False):
         super().__init__()
         if isinstance(normalized_shape, int):
             normalized_shape = (normalized_shape,)
         self.normalized_shape = tuple(normalized_shape)
         self.eps = eps
         self.layer_idx = layer_idx
-        self.weight = create_parameter(self.normalized_shape, ones_, layer_idx=layer_idx, dtype=dtype)
+        self.zero_centered = zero_centered
+        self.weight = create_parameter(self.normalized_shape, zeros_ if zero_centered else ones_, layer_idx=layer_idx, dtype=dtype)
         self.weight.sequence_parallel = dutil.get_dist_util().sequence_parallel
 
     def forward(self, x):
-        return OF.rms_norm(x, self.weight, self.eps)
+        return OF.rms_norm(x, self.weight + 1.0 if self.zero_centered else self.weight, self.eps)
+
+    def rows(self, x, out, ids=None):
+        """Inference form on 2-D row views: ``x`` may be the fp32 residual stream while ``out`` has the compute dtype; with
+        ``ids`` row r reads ``x[ids[r]]`` (embedding lookup fused with the norm)."""
+        from libai_b200.ops import seq_functional as SF
+
+        return SF.rms_norm_rows(x, self.weight, offset=1.0 if self.zero_centered else 0.0, eps=self.eps, out=out, ids=ids)
 
     def extra_repr(self) -> str:
         return f"{self.normalized_shape}, eps={self.eps}"

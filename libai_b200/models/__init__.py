@@ -1,5 +1,6 @@
 from .bert_model import BertForClassification, BertForPreTraining, BertModel
 from .build import build_graph, build_model
+from .bumodra_model import BumodraForCausalLM, BumodraModel
 from .gpt_model import GPTForPreTraining, GPTModel
 from .llama_model import LlamaForCausalLM, LlamaModel
 from .resmlp import ResMLP
@@ -17,4 +18,5 @@ __all__ = [
     "T5Model", "T5ForPreTraining",
     "VisionTransformer", "SwinTransformer", "SwinTransformerV2", "ResMLP",
     "LlamaModel", "LlamaForCausalLM",
+    "BumodraModel", "BumodraForCausalLM",
 ]

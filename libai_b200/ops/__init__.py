@@ -76,6 +76,27 @@ def load_ext(required: bool = True):
     return _EXT
 
 
+_SEQ_EXT = None
+_SEQ_SO_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_C_seq.so")
+
+
+def load_seq_ext():
+    """Load ``libai_b200/_C_seq.so`` (ragged-batch sequence mixers) once; it is compiled in-tree on first use when the
+    checkout has no built copy yet.  Returns the operator namespace ``torch.ops.libai_b200_seq``."""
+    global _SEQ_EXT
+    if _SEQ_EXT is not None:
+        return _SEQ_EXT
+    with _LOCK:
+        if _SEQ_EXT is None:
+            if not os.path.exists(_SEQ_SO_PATH):
+                from . import build as _build
+
+                _build.build(only=["_C_seq"])
+            torch.ops.load_library(_SEQ_SO_PATH)
+            _SEQ_EXT = _FastOps(torch.ops.libai_b200_seq)
+    return _SEQ_EXT
+
+
 def use_native(*tensors) -> bool:
     """True when the native sm_100a kernel must be used for these tensors."""
     if impl() != "native":

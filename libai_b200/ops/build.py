@@ -1,6 +1,7 @@
-"""In-tree build of the native extension ``libai_b200/_C.so`` (and the C++ dataset helpers).
+"""In-tree build of the native extensions: ``libai_b200/_C.so`` (GEMM, attention, norms, optimizer, collectives) and
+``libai_b200/_C_seq.so`` (ragged-batch sequence mixers with per-sequence state).
 
-    python -m libai_b200.ops.build [--force] [--verbose]
+    python -m libai_b200.ops.build [--force] [--verbose] [--only _C|_C_seq]
 
 CUDA sources are compiled for sm_100a only (``-gencode arch=compute_100a,code=sm_100a -lineinfo``);
 nvcc cross-compiles without a GPU.  Objects are cached under ``libai_b200/csrc/build`` keyed by
@@ -24,11 +25,16 @@ NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 
 CU_SOURCES = ["gemm_sm100.cu", "norm.cu", "elementwise.cu", "attention_sm100.cu", "comm_kernels.cu"]
 CPP_SOURCES = ["bindings.cpp", "symm_mem.cpp"]
+SEQ_SO_PATH = os.path.join(ROOT, "_C_seq.so")
+SEQ_CU_SOURCES = ["seq_mixers.cu"]
+SEQ_CPP_SOURCES = ["seq_bindings.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "--use_fast_math", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v",
 ]
+# the sequence mixers promise fp32 results exact to rounding: IEEE division / sqrt / exp, no fast-math
+SEQ_NVCC_FLAGS = [f for f in NVCC_FLAGS if f != "--use_fast_math"]
 
 
 def _run(cmd, verbose):
@@ -47,7 +53,16 @@ def _stale(src, obj, deps=()):
     return any(os.path.getmtime(p) > t for p in (src,) + tuple(deps) if os.path.exists(p))
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, only=None) -> str:
+    """Build the libraries named in ``only`` (default: both); returns the path of ``_C.so``."""
+    if only is None or "_C_seq" in only:
+        _build_lib(SEQ_SO_PATH, SEQ_CU_SOURCES, SEQ_CPP_SOURCES, SEQ_NVCC_FLAGS, "_C_seq", force, verbose)
+    if only is None or "_C" in only:
+        _build_lib(SO_PATH, CU_SOURCES, CPP_SOURCES, NVCC_FLAGS, "_C", force, verbose)
+    return SO_PATH
+
+
+def _build_lib(SO_PATH, CU_SOURCES, CPP_SOURCES, NVCC_FLAGS, ext_name, force, verbose):
     import torch
     from torch.utils import cpp_extension
 
@@ -70,21 +85,23 @@ def build(force: bool = False, verbose: bool = False) -> str:
         objs.append(obj)
         if force or _stale(src, obj, headers):
             jobs.append((s, ["g++", "-O2", "-std=c++17", "-fPIC", f"-D_GLIBCXX_USE_CXX11_ABI={abi}",
-                             "-DTORCH_EXTENSION_NAME=_C", *inc, "-I", os.path.join(CUDA_HOME, "include"),
+                             f"-DTORCH_EXTENSION_NAME={ext_name}", *inc, "-I", os.path.join(CUDA_HOME, "include"),
                              "-I", CSRC, "-c", src, "-o", obj]))
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             for (name, _), out in zip(jobs, ex.map(lambda j: _run(j[1], verbose), jobs)):
                 logs[name] = out
         os.makedirs(os.path.join(os.path.dirname(ROOT), "profiles"), exist_ok=True)
-        with open(os.path.join(BUILD, "ptxas.log"), "w") as f:
+        with open(os.path.join(BUILD, f"ptxas{ext_name}.log"), "w") as f:
             for name, out in logs.items():
                 f.write(f"==== {name}\n{out}\n")
     if jobs or force or not os.path.exists(SO_PATH):
         tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
-        _run(["g++", "-shared", "-o", SO_PATH, *objs, f"-L{tlib}", "-lc10", "-ltorch_cpu", "-ltorch", "-lc10_cuda",
+        tmp_so = f"{SO_PATH}.{os.getpid()}.tmp"         # link beside the target, then rename: a reader never sees half a file
+        _run(["g++", "-shared", "-o", tmp_so, *objs, f"-L{tlib}", "-lc10", "-ltorch_cpu", "-ltorch", "-lc10_cuda",
               "-ltorch_cuda", f"-L{os.path.join(CUDA_HOME, 'lib64')}", "-lcudart",
               f"-Wl,-rpath,{tlib}", f"-Wl,-rpath,{os.path.join(CUDA_HOME, 'lib64')}"], verbose)
+        os.replace(tmp_so, SO_PATH)
     return SO_PATH
 
 
@@ -92,5 +109,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--only", action="append", choices=["_C", "_C_seq"])
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, a.only))
