@@ -150,7 +150,7 @@ class BumodraModel(nn.Module):
         self.embed_norm.rows(self.embed, x, ids=tokens)
         x0 = None
         if self.loop:
-            x0 = x.to(dt)
+            x0 = x.to(dt, copy=True)             # the blocks update x in place
         for run, (i, enters) in enumerate(self.runs):
             if enters:
                 x = SF.linear(torch.cat([x.to(dt), x0], 1), self.loop_in).float()
