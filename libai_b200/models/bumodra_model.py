@@ -194,6 +194,7 @@ class BumodraForCausalLM(nn.Module, Generator):
         """One step of a ragged batch: ``tokens`` ``[rb.tokens]`` int64 on the model's device; advances the state of the
         step's slots.  Returns fp32 logits of the packed rows ``logits_rows`` (default: all), ``[rows, vocab]``."""
         cache = self.state_cache()
+        tokens = tokens.to(self.head.device, torch.long).contiguous()
         x = self.model(tokens, rb, cache, self._handles, tap=tap)
         cache.advance(rb.slot_list, rb.lens)
         if logits_rows is not None:
