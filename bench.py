@@ -79,6 +79,13 @@ def parse_args():
     ap.add_argument("--zero", type=int, default=-1, help="ZeRO stage; -1 = auto (stage 1 with the fused NVLink kernels when dp > 1)")
     ap.add_argument("--acc", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--serving", action="store_true",
+                    help="instead of the training step: prefill / decode throughput of the stateful sequence-mixer model "
+                         "(Bumodra) beside Llama at equal size (libai_b200/inference/serving_bench.py), one GPU")
+    ap.add_argument("--serving-sizes", default="", help="comma separated names of serving_bench.SIZES (default: all)")
+    ap.add_argument("--serving-batch", type=int, default=8)
+    ap.add_argument("--serving-prompt", type=int, default=2048)
+    ap.add_argument("--serving-kernels", action="store_true", help="add the per-kernel device times and roofline fractions")
     ap.add_argument("--graphs", type=int, default=1,
                     help="1 (default = train.cuda_graphs.enabled default): replay the transformer blocks from CUDA graphs "
                          "(data-parallel and fused tensor-parallel layouts; pipeline-parallel runs launch eagerly)")
@@ -559,6 +566,10 @@ class _ExtrasWatchdog:
 
 def main():
     args = parse_args()
+    if args.serving:
+        from libai_b200.inference import serving_bench
+
+        return serving_bench.main(args)
     if args.impl == "reference":
         return run_reference(args)
     if args.impl == "ref":

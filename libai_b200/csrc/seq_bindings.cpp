@@ -21,8 +21,8 @@ int lbs_latent_gather(const void* ring, const void* cnew, const int* ext_seq, co
 int lbs_latent_write(void* ring, const void* cnew, const int* tok_seq, const int* seq_off, const int* slots, const int* past,
                      long tokens, int C, int ring_len, int dtype, cudaStream_t s);
 int lbs_window_attention(const void* q, long ldq, const void* kv, long ldkv, const void* gate, long ldg, const int* tok_seq,
-                         const int* seq_off, const int* ext_off, void* y, long ldy, long tokens, int H, int D, int V, int window,
-                         float scale, int dtype, cudaStream_t s);
+                         const int* seq_off, const int* ext_off, const int* qt_seq, const int* qt_start, int n_qtiles, void* y,
+                         long ldy, long tokens, int H, int D, int V, int window, float scale, int dtype, cudaStream_t s);
 int lbs_latent_decode(const float* qa, const void* ring, const void* cnew, const int* slots, const int* past, float* out, int B, int H,
                       int C, int ring_len, int window, float scale, int dtype, cudaStream_t s);
 int lbs_head_gate(const float* x, const void* gate, long ldg, void* y, long ldy, long rows, int H, int V, int dtype, cudaStream_t s);
@@ -133,7 +133,8 @@ void latent_write(Tensor ring, const Tensor& cnew, const Tensor& tok_seq, const 
 }
 
 void window_attention(const Tensor& q, const Tensor& kv, const c10::optional<Tensor>& gate, const Tensor& tok_seq, const Tensor& seq_off,
-                      const Tensor& ext_off, Tensor y, int64_t H, int64_t D, int64_t V, int64_t window, double scale) {
+                      const Tensor& ext_off, const c10::optional<Tensor>& qt_seq, const c10::optional<Tensor>& qt_start, Tensor y,
+                      int64_t H, int64_t D, int64_t V, int64_t window, double scale) {
   rows2d(q, "window_attention q"); rows2d(kv, "window_attention kv"); rows2d(y, "window_attention y");
   TORCH_CHECK(q.size(1) == H * D && kv.size(1) == H * (D + V) && y.size(1) == H * V && y.size(0) == q.size(0), "window_attention: shapes");
   TORCH_CHECK(code(q) == code(kv) && code(q) == code(y), "window_attention: one dtype expected");
@@ -143,9 +144,15 @@ void window_attention(const Tensor& q, const Tensor& kv, const c10::optional<Ten
     TORCH_CHECK(gate->size(1) == H && gate->size(0) == q.size(0) && code(*gate) == code(q), "window_attention: gate [tokens, H]");
     gp = gate->data_ptr(); ldg = gate->stride(0);
   }
+  const int *qs = nullptr, *qb = nullptr;
+  int nq = 0;
+  if (qt_seq.has_value() && qt_seq->defined() && qt_start.has_value() && qt_start->defined()) {
+    qs = meta(*qt_seq); qb = meta(*qt_start); nq = (int)qt_seq->numel();
+    TORCH_CHECK(qt_start->numel() == nq, "window_attention: query tile lists differ in length");
+  }
   c10::cuda::CUDAGuard guard(q.device());
   check(lbs_window_attention(q.data_ptr(), q.stride(0), kv.data_ptr(), kv.stride(0), gp, ldg, meta(tok_seq), meta(seq_off), meta(ext_off),
-                             y.data_ptr(), y.stride(0), q.size(0), (int)H, (int)D, (int)V, (int)window, (float)scale, code(q),
+                             qs, qb, nq, y.data_ptr(), y.stride(0), q.size(0), (int)H, (int)D, (int)V, (int)window, (float)scale, code(q),
                              cur_stream()), "window_attention");
 }
 
@@ -184,7 +191,7 @@ TORCH_LIBRARY(libai_b200_seq, m) {
   m.def("gated_rmsnorm(Tensor o, Tensor gate, Tensor w, float eps, int act, Tensor(a!) y, int H, int V) -> ()", &gated_rmsnorm);
   m.def("latent_gather(Tensor ring, Tensor cnew, Tensor ext_seq, Tensor ext_off, Tensor seq_off, Tensor slots, Tensor past, Tensor(a!) ext) -> ()", &latent_gather);
   m.def("latent_write(Tensor(a!) ring, Tensor cnew, Tensor tok_seq, Tensor seq_off, Tensor slots, Tensor past) -> ()", &latent_write);
-  m.def("window_attention(Tensor q, Tensor kv, Tensor? gate, Tensor tok_seq, Tensor seq_off, Tensor ext_off, Tensor(a!) y, int H, int D, int V, int window, float scale) -> ()", &window_attention);
+  m.def("window_attention(Tensor q, Tensor kv, Tensor? gate, Tensor tok_seq, Tensor seq_off, Tensor ext_off, Tensor? qt_seq, Tensor? qt_start, Tensor(a!) y, int H, int D, int V, int window, float scale) -> ()", &window_attention);
   m.def("latent_decode(Tensor qa, Tensor ring, Tensor cnew, Tensor slots, Tensor past, Tensor(a!) out, int window, float scale) -> ()", &latent_decode);
   m.def("head_gate(Tensor x, Tensor? gate, Tensor(a!) y, int H, int V) -> ()", &head_gate);
 }

@@ -345,6 +345,140 @@ __global__ void window_attention_kernel(const T* __restrict__ q, long ldq, const
 }
 
 // ------------------------------------------------------------------------------------------------------------------
+// The same attention on the tensor cores (bf16 operands, fp32 accumulation and softmax): a block of 4 warps owns 64
+// consecutive queries of one (sequence, head) — 16 per warp, held as A fragments — and walks the key rows its queries can
+// see in tiles of 64 staged through shared memory: S = Q Kᵀ with mma.m16n8k16, online softmax on the accumulator
+// fragments, P re-packed as A fragments, O += P V with the V fragments fetched by ldmatrix.trans.  Query tiles are
+// listed by the host (qt_seq / qt_start), so ragged batches cost no empty blocks.
+// ------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int D, int V>
+__global__ void __launch_bounds__(128)
+window_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long ldq, const __nv_bfloat16* __restrict__ kv, long ldkv,
+                            const __nv_bfloat16* __restrict__ gate, long ldg, const int* __restrict__ qt_seq,
+                            const int* __restrict__ qt_start, const int* __restrict__ seq_off, const int* __restrict__ ext_off,
+                            __nv_bfloat16* __restrict__ y, long ldy, int H, int window, float scale) {
+  constexpr int KT = 64, KS = D + 8, VS = V + 8;
+  __shared__ __align__(16) __nv_bfloat16 Ks[KT * KS];
+  __shared__ __align__(16) __nv_bfloat16 Vs[KT * VS];
+  const int h = blockIdx.y, b = qt_seq[blockIdx.x], t0 = qt_start[blockIdx.x];
+  const int n = seq_off[b + 1] - seq_off[b];
+  const int elo = ext_off[b], ehi = ext_off[b + 1], npast = ehi - elo - n;
+  const long tokbase = seq_off[b];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+  const int r0 = t0 + warp * 16 + gid, r1 = r0 + 8;                    // this lane's two query rows
+  const int e0 = elo + npast + r0, e1 = e0 + 8;                          // their key rows
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const int col = h * D + kk * 16 + tig * 2;
+    qf[kk][0] = r0 < n ? *reinterpret_cast<const uint32_t*>(q + (tokbase + r0) * ldq + col) : 0u;
+    qf[kk][1] = r1 < n ? *reinterpret_cast<const uint32_t*>(q + (tokbase + r1) * ldq + col) : 0u;
+    qf[kk][2] = r0 < n ? *reinterpret_cast<const uint32_t*>(q + (tokbase + r0) * ldq + col + 8) : 0u;
+    qf[kk][3] = r1 < n ? *reinterpret_cast<const uint32_t*>(q + (tokbase + r1) * ldq + col + 8) : 0u;
+  }
+  float o[V / 8][4];
+#pragma unroll
+  for (int j = 0; j < V / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;              // l: this lane's share of the row sums
+  const int eq_first = elo + npast + t0, eq_last = elo + npast + min(t0 + 63, n - 1);
+  const int ew0 = eq_first + warp * 16;                                   // first key row of this warp's queries
+  int kbeg = eq_first - window + 1;
+  if (kbeg < elo) kbeg = elo;
+  for (int k0 = kbeg; k0 <= eq_last; k0 += KT) {
+    __syncthreads();
+    for (int c = threadIdx.x; c < KT * (D / 8); c += 128) {
+      const int row = c / (D / 8), ch = c - row * (D / 8);
+      uint4 val = make_uint4(0u, 0u, 0u, 0u);
+      if (k0 + row < ehi) val = *reinterpret_cast<const uint4*>(kv + (long)(k0 + row) * ldkv + h * D + ch * 8);
+      *reinterpret_cast<uint4*>(&Ks[row * KS + ch * 8]) = val;
+    }
+    for (int c = threadIdx.x; c < KT * (V / 8); c += 128) {
+      const int row = c / (V / 8), ch = c - row * (V / 8);
+      uint4 val = make_uint4(0u, 0u, 0u, 0u);
+      if (k0 + row < ehi) val = *reinterpret_cast<const uint4*>(kv + (long)(k0 + row) * ldkv + (long)H * D + h * V + ch * 8);
+      *reinterpret_cast<uint4*>(&Vs[row * VS + ch * 8]) = val;
+    }
+    __syncthreads();
+    if (k0 > ew0 + 15 || k0 + KT - 1 <= ew0 - window) continue;          // nothing in this tile for the warp's 16 queries
+    float sacc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f; }
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const __nv_bfloat16* kr = &Ks[(j * 8 + gid) * KS + kk * 16 + tig * 2];
+        mma_bf16(sacc[j], qf[kk], *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 8));
+      }
+    }
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = k0 + j * 8 + tig * 2 + (c & 1), eq = c < 2 ? e0 : e1;
+        const bool valid = key <= eq && key > eq - window;
+        const float sv = valid ? sacc[j][c] * scale : -INFINITY;
+        sacc[j][c] = sv;
+        if (c < 2) mx0 = fmaxf(mx0, sv); else mx1 = fmaxf(mx1, sv);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float c0 = mn0 == -INFINITY ? 1.f : __expf(m0 - mn0), c1 = mn1 == -INFINITY ? 1.f : __expf(m1 - mn1);
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float sv = sacc[j][c];
+        const float pv = sv == -INFINITY ? 0.f : __expf(sv - (c < 2 ? mn0 : mn1));
+        sacc[j][c] = pv;
+        if (c < 2) s0 += pv; else s1 += pv;
+      }
+    }
+    l0 = l0 * c0 + s0; l1 = l1 * c1 + s1; m0 = mn0; m1 = mn1;
+#pragma unroll
+    for (int j = 0; j < V / 8; ++j) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+#pragma unroll
+    for (int k2 = 0; k2 < 4; ++k2) {
+      uint32_t a[4];
+      a[0] = pack_bf16(sacc[2 * k2][0], sacc[2 * k2][1]); a[1] = pack_bf16(sacc[2 * k2][2], sacc[2 * k2][3]);
+      a[2] = pack_bf16(sacc[2 * k2 + 1][0], sacc[2 * k2 + 1][1]); a[3] = pack_bf16(sacc[2 * k2 + 1][2], sacc[2 * k2 + 1][3]);
+      const uint32_t vrow = (uint32_t)__cvta_generic_to_shared(&Vs[(k2 * 16 + (lane & 15)) * VS]);
+#pragma unroll
+      for (int j = 0; j < V / 8; ++j) {
+        uint32_t b0, b1;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(b0), "=r"(b1) : "r"(vrow + j * 16));
+        mma_bf16(o[j], a, b0, b1);
+      }
+    }
+  }
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float g0 = (gate && r0 < n) ? sigmoidf_(__bfloat162float(gate[(tokbase + r0) * ldg + h])) : 1.f;
+  const float g1 = (gate && r1 < n) ? sigmoidf_(__bfloat162float(gate[(tokbase + r1) * ldg + h])) : 1.f;
+  const float i0 = g0 / l0, i1 = g1 / l1;
+#pragma unroll
+  for (int j = 0; j < V / 8; ++j) {
+    const int col = h * V + j * 8 + tig * 2;
+    if (r0 < n) *reinterpret_cast<uint32_t*>(y + (tokbase + r0) * ldy + col) = pack_bf16(o[j][0] * i0, o[j][1] * i0);
+    if (r1 < n) *reinterpret_cast<uint32_t*>(y + (tokbase + r1) * ldy + col) = pack_bf16(o[j][2] * i1, o[j][3] * i1);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
 // Single-token steps in the absorbed form: the query already carries the key up-projection (qa [B, H, C], fp32), so the
 // scores and the weighted sum run on the cached latents themselves; the new token's latent (cnew [B, C]) is position
 // past[b], the others come from the ring.  out: [B, H, C] fp32 = softmax-weighted latent per head (the value
@@ -517,10 +651,23 @@ int lbs_latent_write(void* ring, const void* cnew, const int* tok_seq, const int
 }
 
 int lbs_window_attention(const void* q, long ldq, const void* kv, long ldkv, const void* gate, long ldg, const int* tok_seq,
-                         const int* seq_off, const int* ext_off, void* y, long ldy, long tokens, int H, int D, int V, int window,
-                         float scale, int dtype, cudaStream_t s) {
+                         const int* seq_off, const int* ext_off, const int* qt_seq, const int* qt_start, int n_qtiles, void* y,
+                         long ldy, long tokens, int H, int D, int V, int window, float scale, int dtype, cudaStream_t s) {
   if (tokens == 0) return 0;
   if (V > 32 * ATT_MAXV) return -1;
+  const bool aligned = (ldkv % 8 == 0) && (ldq % 2 == 0) && (ldy % 2 == 0) && (((uintptr_t)kv) % 16 == 0) &&
+                       (((uintptr_t)q) % 4 == 0) && (((uintptr_t)y) % 4 == 0);
+  if (dtype == 1 && qt_seq != nullptr && n_qtiles > 0 && aligned) {
+    dim3 grid((unsigned)n_qtiles, (unsigned)H);
+#define WA(DD, VV)                                                                                                        \
+  if (D == DD && V == VV) {                                                                                                \
+    window_attention_mma_kernel<DD, VV><<<grid, 128, 0, s>>>((const bf16*)q, ldq, (const bf16*)kv, ldkv, (const bf16*)gate, ldg, \
+                                                             qt_seq, qt_start, seq_off, ext_off, (bf16*)y, ldy, H, window, scale); \
+    return ok();                                                                                                           \
+  }
+    WA(32, 32) WA(64, 64) WA(128, 128) WA(64, 128) WA(128, 64) WA(32, 64) WA(64, 32)
+#undef WA
+  }
   const int warps = 4;
   const size_t smem = sizeof(float) * warps * D;
   DISPATCH(dtype, window_attention_kernel<T><<<cdiv(tokens * H, warps), warps * 32, smem, s>>>(

@@ -45,11 +45,21 @@ class RaggedBatch:
         self.seq_off, self.slots, self.past = packed[: B + 1], packed[B + 1: 2 * B + 1], packed[2 * B + 1: 3 * B + 1]
         self.tok_seq = packed[3 * B + 1:]
         self._ext: Dict[int, WindowExt] = {}
+        self._tiles: Dict[int, tuple] = {}
 
     def ext(self, window: int) -> WindowExt:
         if window not in self._ext:
             self._ext[window] = WindowExt(self, window)
         return self._ext[window]
+
+    def query_tiles(self, size: int):
+        """Tiles of ``size`` consecutive new tokens of one sequence: (sequence of every tile, its first token) on the device."""
+        if size not in self._tiles:
+            seq = [b for b, n in enumerate(self.lens) for _ in range(0, n, size)]
+            start = [t for n in self.lens for t in range(0, n, size)]
+            packed = torch.tensor(seq + start, dtype=torch.int32).to(self.device, non_blocking=True)
+            self._tiles[size] = (packed[: len(seq)], packed[len(seq):])
+        return self._tiles[size]
 
     def last_rows(self) -> List[int]:
         """Packed row of every sequence's last new token."""

@@ -178,14 +178,17 @@ def latent_write(ring, cnew, rb):
             ring[slot, (past + t) % L] = cnew[lo + t]
 
 
-def window_attention(q, kv, gate, rb, y, H: int, D: int, V: int, window: int, scale: float):
+def window_attention(q, kv, gate, rb, y, H: int, D: int, V: int, window: int, scale: float, mma: bool = True):
     """Softmax attention of every packed query over the ``window`` rows of ``kv`` (keys ``[H·D]`` then values ``[H·V]`` per
     row, laid out as :func:`latent_gather` orders them) that end at its own row; head ``h`` of the result is multiplied by
-    ``sigmoid(gate[t, h])`` when a gate is given.  Writes ``y`` ``[tokens, H·V]``."""
+    ``sigmoid(gate[t, h])`` when a gate is given.  Writes ``y`` ``[tokens, H·V]``.  bf16 inputs with head sizes the tensor-core
+    kernel is built for (32 / 64 / 128) take it; ``mma=False`` keeps them on the generic kernel (fp32 inputs always are)."""
     ext = rb.ext(window)
     if _native(q):
         count_launch()
-        load_seq_ext().window_attention(q, kv, gate, rb.tok_seq, rb.seq_off, ext.ext_off, y, H, D, V, window, float(scale))
+        tiles = rb.query_tiles(64) if (q.dtype == torch.bfloat16 and mma) else (None, None)
+        load_seq_ext().window_attention(q, kv, gate, rb.tok_seq, rb.seq_off, ext.ext_off, tiles[0], tiles[1], y, H, D, V, window,
+                                        float(scale))
         return y
     for b in range(rb.B):
         lo, n, np_, eo = rb.offsets[b], rb.lens[b], ext.npast[b], ext.offsets[b]

@@ -351,3 +351,21 @@ def test_bfloat16_serving_precision_stays_near_the_oracle(tmp_path):
     from libai_b200 import ops
 
     assert ops.launch_count() > 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D,V,window", [(64, 64, 40), (32, 64, 1), (128, 128, 200), (64, 32, 64), (128, 64, 7)])
+def test_tensor_core_window_attention_equals_the_generic_kernel(D, V, window):
+    g = torch.Generator().manual_seed(D + V + window)
+    H, lens, past = 3, [70, 1, 129, 5], [0, 300, 17, 64]
+    cache_rows = min(max(past), window - 1) + 1
+    rb = RaggedBatch(lens, [0, 1, 2, 3], past, "cuda")
+    T, E = rb.tokens, rb.ext(window).rows
+    q = torch.randn(T, H * D, generator=g).to("cuda", torch.bfloat16)
+    kv = torch.randn(E, H * (D + V), generator=g).to("cuda", torch.bfloat16)
+    gate = torch.randn(T, H, generator=g).to("cuda", torch.bfloat16)
+    a, b = torch.empty(T, H * V, dtype=torch.bfloat16, device="cuda"), torch.empty(T, H * V, dtype=torch.bfloat16, device="cuda")
+    SF.window_attention(q, kv, gate, rb, a, H, D, V, window, 0.2, mma=True)
+    SF.window_attention(q, kv, gate, rb, b, H, D, V, window, 0.2, mma=False)
+    assert cache_rows >= 1 and torch.isfinite(a.float()).all()
+    assert (a.float() - b.float()).abs().max() < 0.03
