@@ -447,6 +447,8 @@ Tensor rope_qkv(const Tensor& qkv, const Tensor& cosv, const Tensor& sinv, int64
                   sinv.is_contiguous() && cosv.size(0) >= S + pos_offset && cosv.size(1) == D &&
                   sinv.sizes() == cosv.sizes(),
               "rope_qkv: cos/sin fp32 [>=S+offset, D]");
+  TORCH_CHECK(qkv.is_cuda() && cosv.device() == qkv.device() && sinv.device() == qkv.device(),
+              "rope_qkv: qkv, cos and sin must be on one CUDA device (move the model's buffers with .to(device))");
   Tensor y = inplace ? qkv : at::empty_like(qkv);
   check(lb_rope_qkv(qkv.data_ptr(), cosv.data_ptr<float>(), sinv.data_ptr<float>(), y.data_ptr(),
                     qkv.numel() / (3 * D), S, A, D, (int)pos_offset, backward ? 1 : 0, cur_stream()),
@@ -459,6 +461,7 @@ Tensor rope(const Tensor& x, const Tensor& cosv, const Tensor& sinv, bool backwa
   TORCH_CHECK(x.dim() == 4 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "rope: contiguous bf16 [b,a,s,d]");
   const int S = (int)x.size(2), D = (int)x.size(3);
   TORCH_CHECK(cosv.is_contiguous() && sinv.is_contiguous() && cosv.size(0) >= S && cosv.size(1) == D, "rope: cos/sin [S,D]");
+  TORCH_CHECK(x.is_cuda() && cosv.device() == x.device() && sinv.device() == x.device(), "rope: x, cos and sin must be on one CUDA device");
   Tensor y = at::empty_like(x);
   check(lb_rope(x.data_ptr(), cosv.data_ptr<float>(), sinv.data_ptr<float>(), y.data_ptr(), x.numel() / D, S, D,
                 backward ? 1 : 0, cur_stream()),

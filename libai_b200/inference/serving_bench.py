@@ -73,7 +73,7 @@ def build_models(s, device="cuda"):
             num_attention_heads=s["heads"] if s["width"] // s["heads"] in (64, 128) else s["width"] // 128,
             max_position_embeddings=8192, rms_norm_eps=1e-6, initializer_range=0.02, use_scaled_init_for_output_weights=True,
             scale_mask_softmax_fusion=False, amp_enabled=False))).eval()
-    return bum, llama
+    return bum.cuda(), llama.cuda()            # .cuda(): the rotary tables are buffers built on the host
 
 
 @torch.no_grad()
