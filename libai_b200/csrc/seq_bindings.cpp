@@ -23,8 +23,9 @@ int lbs_latent_write(void* ring, const void* cnew, const int* tok_seq, const int
 int lbs_window_attention(const void* q, long ldq, const void* kv, long ldkv, const void* gate, long ldg, const int* tok_seq,
                          const int* seq_off, const int* ext_off, const int* qt_seq, const int* qt_start, int n_qtiles, void* y,
                          long ldy, long tokens, int H, int D, int V, int window, float scale, int dtype, cudaStream_t s);
-int lbs_latent_decode(const float* qa, const void* ring, const void* cnew, const int* slots, const int* past, float* out, int B, int H,
-                      int C, int ring_len, int window, float scale, int dtype, cudaStream_t s);
+int lbs_latent_decode(const float* qa, const void* ring, const void* cnew, const int* slots, const int* past, float* out,
+                      float* part_o, float* part_ml, int B, int H, int C, int ring_len, int window, float scale, int dtype,
+                      cudaStream_t s);
 int lbs_head_gate(const float* x, const void* gate, long ldg, void* y, long ldy, long rows, int H, int V, int dtype, cudaStream_t s);
 }
 
@@ -164,8 +165,16 @@ void latent_decode(const Tensor& qa, const Tensor& ring, const Tensor& cnew, con
               cnew.size(1) == qa.size(2) && cnew.size(0) == qa.size(0) && code(ring) == code(cnew), "latent_decode: shapes");
   TORCH_CHECK(ring.size(1) >= window, "latent_decode: the ring is shorter than the window");
   c10::cuda::CUDAGuard guard(qa.device());
+  Tensor part_o, part_ml;
+  float *po = nullptr, *pm = nullptr;
+  if (window > 64) {                                  // long windows: partial softmax per 32 positions, merged afterwards
+    const int64_t nch = (window + 31) / 32;
+    part_o = at::empty({qa.size(0), qa.size(1), nch, qa.size(2)}, qa.options());
+    part_ml = at::empty({qa.size(0), qa.size(1), nch, 2}, qa.options());
+    po = part_o.data_ptr<float>(); pm = part_ml.data_ptr<float>();
+  }
   check(lbs_latent_decode(qa.data_ptr<float>(), ring.data_ptr(), cnew.data_ptr(), meta(slots), meta(past), out.data_ptr<float>(),
-                          (int)qa.size(0), (int)qa.size(1), (int)qa.size(2), (int)ring.size(1), (int)window, (float)scale, code(ring),
+                          po, pm, (int)qa.size(0), (int)qa.size(1), (int)qa.size(2), (int)ring.size(1), (int)window, (float)scale, code(ring),
                           cur_stream()), "latent_decode");
 }
 

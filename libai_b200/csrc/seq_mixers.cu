@@ -125,27 +125,30 @@ __global__ void conv_tail_kernel(const T* __restrict__ in, long ldi, T* __restri
 // Gated delta rule.  Per head, with S [D, V] in fp32:   S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;
 // o = S^T q.  q and k arrive after the convolution, are normalised here to unit length per head (eps inside the
 // root) and q is scaled by D^-1/2.  g = exp(-exp(A_log) softplus(a + dt_bias)) per head (chan == 0) or per key channel
-// (chan == 1); beta = sigmoid(b).  Columns of S are independent: a block owns `VT` of them for one (sequence, head),
-// every column is shared by R lanes that each keep DPT rows (rows i = d R + r) in registers, and tokens are staged
-// through shared memory `CT` at a time so that the serial part only touches registers and shared memory.
+// (chan == 1); beta = sigmoid(b).  Columns of S are independent: a block owns `VT` of them for one (sequence, head);
+// every column is shared by R lanes (R a power of two, adjacent lanes of one warp) that each keep DPT consecutive rows
+// of it in registers, so a token costs 3·DPT fused multiply-adds per lane and log2(R) shuffle rounds.  Tokens are staged
+// through shared memory `CT` at a time (rows of lane r at offset r·(DPT+4): 16-byte loads without bank conflicts), so
+// the serial part only touches registers and shared memory.
 // ------------------------------------------------------------------------------------------------------------------
 constexpr int CT = 16;
 
 template <typename T, int DPT>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(256)
 delta_scan_kernel(const T* __restrict__ qkv, long ldq, int koff, int voff, const T* __restrict__ a, long lda,
                   const T* __restrict__ bl, long ldb, const T* __restrict__ A_log, const T* __restrict__ dt_bias,
                   float* __restrict__ S, const int* __restrict__ seq_off, const int* __restrict__ slots,
                   const int* __restrict__ past, float* __restrict__ out, int H, int KH, int D, int V, int R, int VT, int chan) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
+  constexpr int PS = DPT + 4;                   // padded stride of one lane's rows
   const int b = blockIdx.x / H, h = blockIdx.x % H, kh = h / (H / KH);
   const int j0 = blockIdx.y * VT;
-  const int Dp = R * DPT;                       // padded row count (rows >= D hold zeros)
+  const int Dr = R * DPT;                       // rows covered (rows >= D hold zeros)
+  const int Dp = R * PS;                        // floats per staged token
   float* sk = sm;                               // [CT][Dp]
   float* sq = sk + CT * Dp;                     // [CT][Dp]
-  float* sg = sq + CT * Dp;                     // [CT][chan ? Dp : 1]
-  const int gl = chan ? Dp : 1;
-  float* sv = sg + CT * gl;                     // [CT][VT]
+  float* sg = sq + CT * Dp;                     // [CT][Dp] (chan) or [CT]
+  float* sv = sg + CT * (chan ? Dp : 4);        // [CT][VT]
   float* sbeta = sv + CT * VT;                  // [CT]
   float* skq = sbeta + CT;                      // [CT]
   const int tid = threadIdx.x, nth = blockDim.x;
@@ -157,26 +160,26 @@ delta_scan_kernel(const T* __restrict__ qkv, long ldq, int koff, int voff, const
   float s[DPT];
 #pragma unroll
   for (int d = 0; d < DPT; ++d) {
-    const int i = d * R + r;
+    const int i = r * DPT + d;
     s[d] = (past[b] > 0 && col_ok && i < D) ? Sg[(long)i * V + j] : 0.f;
   }
-  const float decay_rate = chan ? 0.f : expf(ldf(A_log + h));
-  const float rate_c = expf(ldf(A_log + h));
+  const float rate = expf(ldf(A_log + h));
   const float qs = 1.f / sqrtf((float)D);
   for (int c0 = 0; c0 < n; c0 += CT) {
     const int ct = min(CT, n - c0);
     __syncthreads();
-    for (int e = tid; e < ct * Dp; e += nth) {
-      const int t = e / Dp, i = e - t * Dp;
+    for (int e = tid; e < ct * Dr; e += nth) {
+      const int t = e / Dr, i = e - t * Dr;
+      const int pos = t * Dp + (i / DPT) * PS + (i % DPT);
       const long row = tok0 + c0 + t;
       float kv = 0.f, qv = 0.f, gv = 1.f;
       if (i < D) {
         qv = ldf(qkv + row * ldq + kh * D + i);
         kv = ldf(qkv + row * ldq + koff + kh * D + i);
-        if (chan) gv = expf(-rate_c * softplusf_(ldf(a + row * lda + h * D + i) + ldf(dt_bias + h * D + i)));
+        if (chan) gv = expf(-rate * softplusf_(ldf(a + row * lda + h * D + i) + ldf(dt_bias + h * D + i)));
       }
-      sk[e] = kv; sq[e] = qv;
-      if (chan) sg[e] = gv;
+      sk[pos] = kv; sq[pos] = qv;
+      if (chan) sg[pos] = gv;
     }
     for (int e = tid; e < ct * VT; e += nth) {
       const int t = e / VT, c = e - t * VT;
@@ -185,19 +188,23 @@ delta_scan_kernel(const T* __restrict__ qkv, long ldq, int koff, int voff, const
     for (int t = tid; t < ct; t += nth) {
       const long row = tok0 + c0 + t;
       sbeta[t] = sigmoidf_(ldf(bl + row * ldb + h));
-      if (!chan) sg[t] = expf(-decay_rate * softplusf_(ldf(a + row * lda + h) + ldf(dt_bias + h)));
+      if (!chan) sg[t] = expf(-rate * softplusf_(ldf(a + row * lda + h) + ldf(dt_bias + h)));
     }
     __syncthreads();
     // unit length per token: one warp per token
     for (int t = tid >> 5; t < ct; t += nth >> 5) {
       float kk = 0.f, qq = 0.f;
-      for (int i = tid & 31; i < Dp; i += 32) { kk += sk[t * Dp + i] * sk[t * Dp + i]; qq += sq[t * Dp + i] * sq[t * Dp + i]; }
+      for (int i = tid & 31; i < Dr; i += 32) {
+        const int pos = t * Dp + (i / DPT) * PS + (i % DPT);
+        kk += sk[pos] * sk[pos]; qq += sq[pos] * sq[pos];
+      }
       kk = warp_sum(kk); qq = warp_sum(qq);
       const float ksc = 1.f / sqrtf(kk + 1e-6f), qsc = qs / sqrtf(qq + 1e-6f);
       float kq = 0.f;
-      for (int i = tid & 31; i < Dp; i += 32) {
-        const float kx = sk[t * Dp + i] * ksc, qx = sq[t * Dp + i] * qsc;
-        sk[t * Dp + i] = kx; sq[t * Dp + i] = qx; kq += kx * qx;
+      for (int i = tid & 31; i < Dr; i += 32) {
+        const int pos = t * Dp + (i / DPT) * PS + (i % DPT);
+        const float kx = sk[pos] * ksc, qx = sq[pos] * qsc;
+        sk[pos] = kx; sq[pos] = qx; kq += kx * qx;
       }
       kq = warp_sum(kq);
       if ((tid & 31) == 0) skq[t] = kq;
@@ -205,24 +212,33 @@ delta_scan_kernel(const T* __restrict__ qkv, long ldq, int koff, int voff, const
     __syncthreads();
     // every thread walks the tokens (lanes of idle columns included: the shuffles below name the whole warp)
     for (int t = 0; t < ct; ++t) {
-      float pk = 0.f, pq = 0.f;
-      const float* kt = sk + t * Dp; const float* qt = sq + t * Dp; const float* gt = sg + t * gl;
+      float kr[DPT];
+      float pk[4] = {0.f, 0.f, 0.f, 0.f}, pq[4] = {0.f, 0.f, 0.f, 0.f};
+      const float4* k4 = reinterpret_cast<const float4*>(sk + t * Dp + r * PS);
+      const float4* q4 = reinterpret_cast<const float4*>(sq + t * Dp + r * PS);
+      const float4* g4 = reinterpret_cast<const float4*>(sg + t * Dp + r * PS);
+      const float g0 = chan ? 1.f : sg[t];
 #pragma unroll
-      for (int d = 0; d < DPT; ++d) {
-        const int i = d * R + r;
-        s[d] *= chan ? gt[i] : gt[0];
-        pk += s[d] * kt[i]; pq += s[d] * qt[i];
+      for (int d4 = 0; d4 < DPT / 4; ++d4) {
+        const float4 kx = k4[d4], qx = q4[d4];
+        float4 gx = make_float4(g0, g0, g0, g0);
+        if (chan) gx = g4[d4];
+        kr[4 * d4] = kx.x; kr[4 * d4 + 1] = kx.y; kr[4 * d4 + 2] = kx.z; kr[4 * d4 + 3] = kx.w;
+        s[4 * d4] *= gx.x; s[4 * d4 + 1] *= gx.y; s[4 * d4 + 2] *= gx.z; s[4 * d4 + 3] *= gx.w;
+        pk[0] += s[4 * d4] * kx.x; pk[1] += s[4 * d4 + 1] * kx.y; pk[2] += s[4 * d4 + 2] * kx.z; pk[3] += s[4 * d4 + 3] * kx.w;
+        pq[0] += s[4 * d4] * qx.x; pq[1] += s[4 * d4 + 1] * qx.y; pq[2] += s[4 * d4 + 2] * qx.z; pq[3] += s[4 * d4 + 3] * qx.w;
       }
-      for (int m = R >> 1; m > 0; m >>= 1) { pk += __shfl_xor_sync(0xffffffffu, pk, m); pq += __shfl_xor_sync(0xffffffffu, pq, m); }
-      const float u = sbeta[t] * ((jj < VT ? sv[t * VT + jj] : 0.f) - pk);
+      float sk_ = (pk[0] + pk[1]) + (pk[2] + pk[3]), sq_ = (pq[0] + pq[1]) + (pq[2] + pq[3]);
+      for (int m = R >> 1; m > 0; m >>= 1) { sk_ += __shfl_xor_sync(0xffffffffu, sk_, m); sq_ += __shfl_xor_sync(0xffffffffu, sq_, m); }
+      const float u = sbeta[t] * ((jj < VT ? sv[t * VT + jj] : 0.f) - sk_);
 #pragma unroll
-      for (int d = 0; d < DPT; ++d) s[d] += kt[d * R + r] * u;
-      if (r == 0 && col_ok) out[(tok0 + c0 + t) * (long)(H * V) + h * V + j] = pq + skq[t] * u;
+      for (int d = 0; d < DPT; ++d) s[d] += kr[d] * u;
+      if (r == 0 && col_ok) out[(tok0 + c0 + t) * (long)(H * V) + h * V + j] = sq_ + skq[t] * u;
     }
   }
   if (col_ok) {
 #pragma unroll
-    for (int d = 0; d < DPT; ++d) { const int i = d * R + r; if (i < D) Sg[(long)i * V + j] = s[d]; }
+    for (int d = 0; d < DPT; ++d) { const int i = r * DPT + d; if (i < D) Sg[(long)i * V + j] = s[d]; }
   }
 }
 
@@ -533,6 +549,85 @@ __global__ void latent_decode_kernel(const float* __restrict__ qa, const T* __re
   for (int i = 0; i < ABS_MAXC; ++i) { const int c = lane + 32 * i; if (c < C) out[((long)b * H + h) * C + c] = acc[i] * inv; }
 }
 
+// Split form of the same step for long windows: all heads of a sequence share its latents, so a block stages KC = 32
+// of them once (plus the queries of up to 16 heads) in shared memory, computes the scores of every head against them,
+// a partial softmax (max, sum) and the partial weighted sum; a second kernel merges the partials of a (sequence, head).
+constexpr int KC = 32, HG = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_decode_split_kernel(const float* __restrict__ qa, const T* __restrict__ ring, const T* __restrict__ cnew,
+                           const int* __restrict__ slots, const int* __restrict__ past, float* __restrict__ part_o,
+                           float* __restrict__ part_ml, int H, int C, int ring_len, int window, int nch, float scale) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int b = blockIdx.x, ch = blockIdx.y, h0 = blockIdx.z * HG;
+  const int hg = min(HG, H - h0);
+  const int p = past[b];
+  int p0 = p - window + 1; if (p0 < 0) p0 = 0;
+  const int e0 = p0 + ch * KC;
+  if (e0 > p) return;                                           // the whole block leaves: no barrier is skipped
+  const int cnt = min(KC, p - e0 + 1);
+  const int LS = C + (sizeof(T) == 2 ? 2 : 1);                  // tile row stride: an odd number of 32-bit words
+  float* sq = reinterpret_cast<float*>(smraw);                  // [HG][C]
+  float* ss = sq + HG * C;                                      // [HG][KC]
+  T* sl = reinterpret_cast<T*>(ss + HG * KC);                   // [KC][LS]
+  const int tid = threadIdx.x;
+  for (int e = tid; e < hg * C; e += 256) sq[e] = qa[((long)b * H + h0) * C + e] * scale;
+  const T* rb = ring + (long)slots[b] * ring_len * C;
+  for (int e = tid; e < cnt * C; e += 256) {
+    const int kk = e / C, c = e - kk * C, pos = e0 + kk;
+    sl[kk * LS + c] = pos == p ? cnew[(long)b * C + c] : rb[(long)(pos % ring_len) * C + c];
+  }
+  __syncthreads();
+  const int lane = tid & 31, w = tid >> 5;
+  for (int hh = w; hh < hg; hh += 8) {                          // one warp per head: lane = key
+    float sc = -INFINITY;
+    if (lane < cnt) {
+      float d = 0.f;
+      const float* qr = sq + hh * C; const T* lr = sl + lane * LS;
+      for (int c = 0; c < C; ++c) d += qr[c] * ldf(lr + c);
+      sc = d;
+    }
+    const float m = warp_max(sc);
+    const float pr = lane < cnt ? expf(sc - m) : 0.f;
+    const float l = warp_sum(pr);
+    ss[hh * KC + lane] = pr;
+    if (lane == 0) { float* ml = part_ml + (((long)b * H + h0 + hh) * nch + ch) * 2; ml[0] = m; ml[1] = l; }
+  }
+  __syncthreads();
+  for (int c = tid; c < C; c += 256) {
+    float acc[HG];
+#pragma unroll
+    for (int hh = 0; hh < HG; ++hh) acc[hh] = 0.f;
+    for (int kk = 0; kk < cnt; ++kk) {
+      const float lv = ldf(sl + kk * LS + c);
+#pragma unroll
+      for (int hh = 0; hh < HG; ++hh) acc[hh] += ss[hh * KC + kk] * lv;   // rows >= hg hold stale values that are not stored
+    }
+#pragma unroll
+    for (int hh = 0; hh < HG; ++hh)
+      if (hh < hg) part_o[(((long)b * H + h0 + hh) * nch + ch) * C + c] = acc[hh];
+  }
+}
+
+__global__ void latent_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                           const int* __restrict__ past, float* __restrict__ out, int H, int C, int window, int nch) {
+  const int b = blockIdx.x / H;
+  const int p = past[b];
+  int p0 = p - window + 1; if (p0 < 0) p0 = 0;
+  const int used = (p - p0) / KC + 1;
+  const float* ml = part_ml + (long)blockIdx.x * nch * 2;
+  float M = -INFINITY;
+  for (int c = 0; c < used; ++c) M = fmaxf(M, ml[2 * c]);
+  float L = 0.f;
+  for (int c = 0; c < used; ++c) L += expf(ml[2 * c] - M) * ml[2 * c + 1];
+  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+    float acc = 0.f;
+    for (int c = 0; c < used; ++c) acc += expf(ml[2 * c] - M) * part_o[((long)blockIdx.x * nch + c) * C + i];
+    out[(long)blockIdx.x * C + i] = acc / L;
+  }
+}
+
 // y[b, h*V + v] = x[b, h, v] * sigmoid(gate[b, h]) (fp32 in, T out)
 template <typename T>
 __global__ void head_gate_kernel(const float* __restrict__ x, const T* __restrict__ gate, long ldg, T* __restrict__ y, long ldy,
@@ -604,14 +699,14 @@ int lbs_delta_scan(const void* qkv, long ldq, int koff, int voff, const void* a,
                    int KH, int D, int V, int chan, int dtype, cudaStream_t s) {
   if (B == 0) return 0;
   if (D > 256 || H % KH != 0) return -1;
-  const int dpt = D <= 128 ? 4 : 8;
+  const int dpt = D <= 32 ? 8 : (D <= 64 ? 16 : 32);   // rows per lane; R = 4 lanes per column up to D = 128, 8 up to 256
   int R = 1;
-  while (R * dpt < D) R <<= 1;                   // lanes per column, a power of two <= 32
-  int VT = V < 1024 / R ? V : 1024 / R;          // columns per block
-  if (VT > 64) VT = 64;                          // more blocks per head: columns are independent
+  while (R * dpt < D) R <<= 1;                   // a power of two <= 8
+  int VT = R <= 4 ? 64 : 32;                     // columns per block (columns are independent: more blocks per head)
+  if (V < VT) VT = V;
   int threads = ((VT * R + 31) / 32) * 32;
-  const int Dp = R * dpt;
-  const size_t smem = sizeof(float) * ((size_t)CT * Dp * 2 + (size_t)CT * (chan ? Dp : 1) + (size_t)CT * VT + 2 * CT);
+  const int Dp = R * (dpt + 4);
+  const size_t smem = sizeof(float) * ((size_t)CT * Dp * 2 + (size_t)CT * (chan ? Dp : 4) + (size_t)CT * VT + 2 * CT);
   dim3 grid((unsigned)(B * H), (unsigned)((V + VT - 1) / VT));
 #define DS(TT, P)                                                                                                              \
   {                                                                                                                            \
@@ -620,8 +715,8 @@ int lbs_delta_scan(const void* qkv, long ldq, int koff, int voff, const void* a,
                                                         (const TT*)A_log, (const TT*)dt_bias, S, seq_off, slots, past, out, H, KH, \
                                                         D, V, R, VT, chan);                                                      \
   }
-  if (dtype == 0) { if (dpt == 4) DS(float, 4) else DS(float, 8) }
-  else { if (dpt == 4) DS(bf16, 4) else DS(bf16, 8) }
+  if (dtype == 0) { if (dpt == 8) DS(float, 8) else if (dpt == 16) DS(float, 16) else DS(float, 32) }
+  else { if (dpt == 8) DS(bf16, 8) else if (dpt == 16) DS(bf16, 16) else DS(bf16, 32) }
 #undef DS
   return ok();
 }
@@ -676,9 +771,29 @@ int lbs_window_attention(const void* q, long ldq, const void* kv, long ldkv, con
   return ok();
 }
 
-int lbs_latent_decode(const float* qa, const void* ring, const void* cnew, const int* slots, const int* past, float* out, int B, int H,
-                      int C, int ring_len, int window, float scale, int dtype, cudaStream_t s) {
+// part_o: [B, H, nch, C] fp32 and part_ml: [B, H, nch, 2] fp32 workspaces with nch = ceil(window / 32), or null: then (and for
+// windows of at most 64 positions) one warp per (sequence, head) does the whole window
+int lbs_latent_decode(const float* qa, const void* ring, const void* cnew, const int* slots, const int* past, float* out,
+                      float* part_o, float* part_ml, int B, int H, int C, int ring_len, int window, float scale, int dtype,
+                      cudaStream_t s) {
   if (B == 0) return 0;
+  if (part_o != nullptr && part_ml != nullptr && window > 64) {
+    const int nch = (window + KC - 1) / KC;
+    const int hg = H < HG ? H : HG;
+    const size_t esz = dtype == 0 ? 4 : 2;
+    const size_t smem = sizeof(float) * ((size_t)HG * C + HG * KC) + esz * KC * (C + (dtype == 0 ? 1 : 2));
+    (void)hg;
+    if (smem <= 200 * 1024) {
+      dim3 grid((unsigned)B, (unsigned)nch, (unsigned)((H + HG - 1) / HG));
+      DISPATCH(dtype, {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(latent_decode_split_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        latent_decode_split_kernel<T><<<grid, 256, smem, s>>>(qa, (const T*)ring, (const T*)cnew, slots, past, part_o, part_ml, H, C,
+                                                              ring_len, window, nch, scale);
+      });
+      latent_decode_merge_kernel<<<B * H, 128, 0, s>>>(part_o, part_ml, past, out, H, C, window, nch);
+      return ok();
+    }
+  }
   if (C > 32 * ABS_MAXC) return -1;
   const int warps = 4;
   const size_t smem = sizeof(float) * warps * C;

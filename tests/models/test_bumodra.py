@@ -369,3 +369,20 @@ def test_tensor_core_window_attention_equals_the_generic_kernel(D, V, window):
     SF.window_attention(q, kv, gate, rb, b, H, D, V, window, 0.2, mma=False)
     assert cache_rows >= 1 and torch.isfinite(a.float()).all()
     assert (a.float() - b.float()).abs().max() < 0.03
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_long_window_single_token_steps(device):
+    # a window of more than 64 positions takes the split single-token kernel on the GPU (partial softmax per 32 positions)
+    lc = O.attention_cfg(heads=5, dim=8, vdim=8, q_rank=8, kv_rank=24, window=70, scale=1.0, ff=0)
+    w = O.random_weights(O.model_cfg([lc], width=16), seed=13)
+    with param_defaults(dtype=torch.float32, device=device):
+        att = LatentAttention(16, 5, 8, 8, 8, 24, 70, scale=1.0, eps=1e-5)
+    _fill(att, w, "l0.mix.")
+    bufs = _state(SequenceStateCache(device, torch.float32), att)
+    T = 110
+    h = torch.randn(T, 16, generator=torch.Generator().manual_seed(14))
+    want = O.latent_attention(h.double(), {k: v.double() for k, v in w.items()}, "l0.mix.", lc["mixer"], 1e-5)
+    parts = [att(h[:3].to(device), _one_sequence(device, 3), bufs).cpu()]
+    parts += [att(h[t:t + 1].to(device), _one_sequence(device, 1, t), bufs).cpu() for t in range(3, T)]
+    assert torch.allclose(torch.cat(parts).double(), want, atol=2e-5, rtol=1e-4)
