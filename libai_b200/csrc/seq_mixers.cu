@@ -134,7 +134,7 @@ __global__ void conv_tail_kernel(const T* __restrict__ in, long ldi, T* __restri
 constexpr int CT = 16;
 
 template <typename T, int DPT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 1)
 delta_scan_kernel(const T* __restrict__ qkv, long ldq, int koff, int voff, const T* __restrict__ a, long lda,
                   const T* __restrict__ bl, long ldb, const T* __restrict__ A_log, const T* __restrict__ dt_bias,
                   float* __restrict__ S, const int* __restrict__ seq_off, const int* __restrict__ slots,

@@ -386,3 +386,34 @@ def test_long_window_single_token_steps(device):
     parts = [att(h[:3].to(device), _one_sequence(device, 3), bufs).cpu()]
     parts += [att(h[t:t + 1].to(device), _one_sequence(device, 1, t), bufs).cpu() for t in range(3, T)]
     assert torch.allclose(torch.cat(parts).double(), want, atol=2e-5, rtol=1e-4)
+
+
+def test_command_line_generation_and_lazy_config(tmp_path, capsys):
+    import importlib.util
+
+    from libai_b200.config import LazyConfig, instantiate
+
+    cfg = mixed_cfg()
+    weights = O.random_weights(cfg, seed=2)
+    folder = save_model(tmp_path, cfg, weights)
+    spec = importlib.util.spec_from_file_location("generate_tool", os.path.join(os.path.dirname(__file__), "..", "..", "tools", "generate.py"))
+    tool = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(tool)
+    out = tool.main(["--model", folder, "--prompts", "5 17 3;9 9 12 40 2", "--max-new-tokens", "4", "--dtype", "float32", "--device", "cpu"])
+    assert out == [O.greedy(cfg, weights, [5, 17, 3], 4), O.greedy(cfg, weights, [9, 9, 12, 40, 2], 4)]
+    assert len(capsys.readouterr().out.strip().splitlines()) == 2
+    node = LazyConfig.load(os.path.join(os.path.dirname(__file__), "..", "..", "configs", "common", "models", "bumodra.py")).model
+    node.cfg.width, node.cfg.vocab = 64, 100
+    for lc in node.cfg.layers:
+        lc["mlp"]["ff"] = 32
+        lc["mixer"].update(heads=2, dim=8, vdim=8)
+        if "kv_heads" in lc["mixer"]:
+            lc["mixer"]["kv_heads"] = 2 if lc["type"] == "channel_delta" else 1
+        for k in ("q_rank", "kv_rank", "decay_rank", "gate_rank"):
+            if k in lc["mixer"]:
+                lc["mixer"][k] = 8
+    with param_defaults(dtype=torch.float32, device="cpu"):
+        model = instantiate(node).eval()
+    ids = torch.randint(3, 100, (2, 7))
+    a = model.generate(ids, max_new_tokens=3)
+    assert a.shape == (2, 10) and torch.equal(a, model.generate(ids, max_new_tokens=3, use_cache=False))
