@@ -77,6 +77,28 @@ __global__ void slice_act_kernel(const Tin* __restrict__ in, long ldi, Tout* __r
   stf(out + r * ldo + c, v);
 }
 
+// the same on bf16 with 16-byte accesses: 8 columns per thread (n, both row strides and both base addresses multiples of 8 elements)
+__global__ void slice_act_vec8_kernel(const __nv_bfloat16* __restrict__ in, long ldi, __nv_bfloat16* __restrict__ out, long ldo,
+                                      long rows, int n8, int act) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * n8) return;
+  const long r = idx / n8; const int c = (int)(idx - r * n8) * 8;
+  uint4 raw = *reinterpret_cast<const uint4*>(in + r * ldi + c);
+  __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 v = __bfloat1622float2(h2[i]);
+    if (act == 1) { v.x = fmaxf(v.x, 0.f); v.x *= v.x; v.y = fmaxf(v.y, 0.f); v.y *= v.y; }
+    else if (act == 2) { v.x = v.x * sigmoidf_(v.x); v.y = v.y * sigmoidf_(v.y); }
+    else if (act == 3) {
+      v.x = 0.5f * v.x * (1.f + tanhf(0.7978845608028654f * (v.x + 0.044715f * v.x * v.x * v.x)));
+      v.y = 0.5f * v.y * (1.f + tanhf(0.7978845608028654f * (v.y + 0.044715f * v.y * v.y * v.y)));
+    }
+    h2[i] = __floats2bfloat162_rn(v.x, v.y);
+  }
+  *reinterpret_cast<uint4*>(out + r * ldo + c) = raw;
+}
+
 // ------------------------------------------------------------------------------------------------------------------
 // Short causal convolution per channel + SiLU.  in: [tokens, ldi] (C channels from column 0), w: [C, taps] with the
 // last tap on the current token, tail: [slots, taps-1, C] = the last taps-1 inputs of every sequence.
@@ -134,7 +156,7 @@ __global__ void conv_tail_kernel(const T* __restrict__ in, long ldi, T* __restri
 constexpr int CT = 16;
 
 template <typename T, int DPT>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(256, DPT <= 16 ? 2 : 1)   // two blocks per SM where 128 registers hold the rows
 delta_scan_kernel(const T* __restrict__ qkv, long ldq, int koff, int voff, const T* __restrict__ a, long lda,
                   const T* __restrict__ bl, long ldb, const T* __restrict__ A_log, const T* __restrict__ dt_bias,
                   float* __restrict__ S, const int* __restrict__ seq_off, const int* __restrict__ slots,
@@ -674,6 +696,10 @@ int lbs_rmsnorm(const void* x, long ldx, int xdtype, const int64_t* ids, const v
 
 int lbs_slice_act(const void* in, long ldi, int idtype, void* out, long ldo, int odtype, long rows, int n, int act, cudaStream_t s) {
   if (rows * n == 0) return 0;
+  if (idtype == 1 && odtype == 1 && n % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)in) % 16 == 0 && ((uintptr_t)out) % 16 == 0) {
+    slice_act_vec8_kernel<<<cdiv(rows * (n / 8), 256), 256, 0, s>>>((const bf16*)in, ldi, (bf16*)out, ldo, rows, n / 8, act);
+    return ok();
+  }
   const int g = cdiv(rows * n, 256);
   if (idtype == 0 && odtype == 0) slice_act_kernel<float, float><<<g, 256, 0, s>>>((const float*)in, ldi, (float*)out, ldo, rows, n, act);
   else if (idtype == 0) slice_act_kernel<float, bf16><<<g, 256, 0, s>>>((const float*)in, ldi, (bf16*)out, ldo, rows, n, act);
@@ -699,7 +725,7 @@ int lbs_delta_scan(const void* qkv, long ldq, int koff, int voff, const void* a,
                    int KH, int D, int V, int chan, int dtype, cudaStream_t s) {
   if (B == 0) return 0;
   if (D > 256 || H % KH != 0) return -1;
-  const int dpt = D <= 32 ? 8 : (D <= 64 ? 16 : 32);   // rows per lane; R = 4 lanes per column up to D = 128, 8 up to 256
+  const int dpt = D <= 32 ? 8 : (D <= 128 ? 16 : 32);  // rows per lane: 4 lanes per column up to D = 64, 8 lanes up to 256
   int R = 1;
   while (R * dpt < D) R <<= 1;                   // a power of two <= 8
   int VT = R <= 4 ? 64 : 32;                     // columns per block (columns are independent: more blocks per head)

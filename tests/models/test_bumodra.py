@@ -417,3 +417,19 @@ def test_command_line_generation_and_lazy_config(tmp_path, capsys):
     ids = torch.randint(3, 100, (2, 7))
     a = model.generate(ids, max_new_tokens=3)
     assert a.shape == (2, 10) and torch.equal(a, model.generate(ids, max_new_tokens=3, use_cache=False))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("act", [SF.ACT_COPY, SF.ACT_RELU2, SF.ACT_SILU, SF.ACT_GELU_TANH])
+def test_slice_activation_between_column_slices(act):
+    x = torch.randn(37, 96, device="cuda").to(torch.bfloat16)
+    wide = torch.zeros(37, 128, dtype=torch.bfloat16, device="cuda")
+    SF.slice_act(x[:, 16:80], wide[:, 32:96], act)               # 16-byte path: offsets and widths are multiples of 8
+    odd = torch.zeros(37, 50, dtype=torch.bfloat16, device="cuda")
+    SF.slice_act(x[:, 3:40], odd[:, 5:42], act)                  # element path
+    v = x.float()
+    want = {SF.ACT_COPY: v, SF.ACT_RELU2: torch.relu(v) ** 2, SF.ACT_SILU: torch.nn.functional.silu(v),
+            SF.ACT_GELU_TANH: torch.nn.functional.gelu(v, approximate="tanh")}[act]
+    assert torch.allclose(wide[:, 32:96].float(), want[:, 16:80], atol=2e-2, rtol=2e-2)
+    assert torch.allclose(odd[:, 5:42].float(), want[:, 3:40], atol=2e-2, rtol=2e-2)
+    assert float(wide[:, :32].abs().max()) == 0 and float(wide[:, 96:].abs().max()) == 0
