@@ -12,8 +12,8 @@ int lbs_slice_act(const void* in, long ldi, int idtype, void* out, long ldo, int
 int lbs_short_conv(const void* in, long ldi, const void* w, void* tail, const int* tok_seq, const int* seq_off, const int* slots,
                    const int* past, void* out, long ldo, long tokens, int B, int C, int taps, int dtype, cudaStream_t s);
 int lbs_delta_scan(const void* qkv, long ldq, int koff, int voff, const void* a, long lda, const void* bl, long ldb, const void* A_log,
-                   const void* dt_bias, float* S, const int* seq_off, const int* slots, const int* past, float* out, int B, int H,
-                   int KH, int D, int V, int chan, int dtype, cudaStream_t s);
+                   const void* dt_bias, float* S, const int* seq_off, const int* slots, const int* past, float* out, float* work,
+                   long tokens, int B, int H, int KH, int D, int V, int chan, int dtype, cudaStream_t s);
 int lbs_gated_rmsnorm(const float* o, const void* gate, long ldg, const void* w, float eps, int act, void* y, long ldy, long rows,
                       int H, int V, int dtype, cudaStream_t s);
 int lbs_latent_gather(const void* ring, const void* cnew, const int* ext_seq, const int* ext_off, const int* seq_off, const int* slots,
@@ -99,9 +99,11 @@ void delta_scan(const Tensor& qkv, int64_t koff, int64_t voff, const Tensor& a, 
               "delta_scan: one dtype expected");
   TORCH_CHECK(A_log.is_contiguous() && dt_bias.is_contiguous(), "delta_scan: contiguous constants");
   c10::cuda::CUDAGuard guard(qkv.device());
+  const int64_t tokens = qkv.size(0);
+  Tensor work = at::empty({tokens * (2 * KH * D + KH + H + (chan ? (int64_t)H * D : (int64_t)H))}, out.options());
   check(lbs_delta_scan(qkv.data_ptr(), qkv.stride(0), (int)koff, (int)voff, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0),
                        A_log.data_ptr(), dt_bias.data_ptr(), S.data_ptr<float>(), meta(seq_off), meta(slots), meta(past),
-                       out.data_ptr<float>(), (int)slots.numel(), H, (int)KH, D, V, chan ? 1 : 0, code(qkv), cur_stream()), "delta_scan");
+                       out.data_ptr<float>(), work.data_ptr<float>(), tokens, (int)slots.numel(), H, (int)KH, D, V, chan ? 1 : 0, code(qkv), cur_stream()), "delta_scan");
 }
 
 void gated_rmsnorm(const Tensor& o, const Tensor& gate, const Tensor& w, double eps, int64_t act, Tensor y, int64_t H, int64_t V) {

@@ -125,6 +125,39 @@ __global__ void short_conv_kernel(const T* __restrict__ in, long ldi, const T* _
   stf(out + tok * ldo + c, acc * sigmoidf_(acc));
 }
 
+// bf16 with 16-byte accesses: a thread owns 8 adjacent channels of one token (C, the row strides and the base addresses are
+// multiples of 8 elements; taps <= 8)
+__global__ void short_conv_vec8_kernel(const __nv_bfloat16* __restrict__ in, long ldi, const __nv_bfloat16* __restrict__ w,
+                                       const __nv_bfloat16* __restrict__ tail, const int* __restrict__ tok_seq,
+                                       const int* __restrict__ seq_off, const int* __restrict__ slots, const int* __restrict__ past,
+                                       __nv_bfloat16* __restrict__ out, long ldo, long tokens, int C, int taps) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int C8 = C >> 3;
+  if (idx >= tokens * C8) return;
+  const long tok = idx / C8; const int c = (int)(idx - tok * C8) * 8;
+  const int b = tok_seq[tok];
+  const int t = (int)(tok - seq_off[b]);
+  const bool has_past = past[b] > 0;
+  const __nv_bfloat16* tl = tail + (long)slots[b] * (taps - 1) * C;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int k = 0; k < taps; ++k) {
+    const int tp = t - k;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (tp >= 0) raw = *reinterpret_cast<const uint4*>(in + (tok - k) * ldi + c);
+    else if (has_past) raw = *reinterpret_cast<const uint4*>(tl + (long)(taps - 1 + tp) * C + c);
+    const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += __bfloat162float(w[(long)(c + i) * taps + (taps - 1 - k)]) * __bfloat162float(x[i]);
+  }
+  uint4 res;
+  __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) r2[i] = __floats2bfloat162_rn(acc[2 * i] * sigmoidf_(acc[2 * i]), acc[2 * i + 1] * sigmoidf_(acc[2 * i + 1]));
+  *reinterpret_cast<uint4*>(out + tok * ldo + c) = res;
+}
+
 template <typename T>
 __global__ void conv_tail_kernel(const T* __restrict__ in, long ldi, T* __restrict__ tail, const int* __restrict__ seq_off,
                                  const int* __restrict__ slots, const int* __restrict__ past, int B, int C, int taps) {
@@ -149,16 +182,55 @@ __global__ void conv_tail_kernel(const T* __restrict__ in, long ldi, T* __restri
 // root) and q is scaled by D^-1/2.  g = exp(-exp(A_log) softplus(a + dt_bias)) per head (chan == 0) or per key channel
 // (chan == 1); beta = sigmoid(b).  Columns of S are independent: a block owns `VT` of them for one (sequence, head);
 // every column is shared by R lanes (R a power of two, adjacent lanes of one warp) that each keep DPT consecutive rows
-// of it in registers, so a token costs 3·DPT fused multiply-adds per lane and log2(R) shuffle rounds.  Tokens are staged
+// of it in registers, so a token costs 3·DPT fused multiply-adds per lane and log2(R) shuffle rounds.  A first kernel
+// prepares the per-token quantities (unit vectors, decays, write strengths) once; the scan stages them
 // through shared memory `CT` at a time (rows of lane r at offset r·(DPT+4): 16-byte loads without bank conflicts), so
 // the serial part only touches registers and shared memory.
 // ------------------------------------------------------------------------------------------------------------------
 constexpr int CT = 16;
 
+// Per token: unit-length keys and queries (queries also times D^-1/2) per key head in fp32, their dot product, the write
+// strength beta = sigmoid(b) and the decay g per head (or per head and key channel).  One warp per (token, key head);
+// the value heads of a group share its work.
+template <typename T>
+__global__ void delta_prep_kernel(const T* __restrict__ qkv, long ldq, int koff, const T* __restrict__ a, long lda,
+                                  const T* __restrict__ bl, long ldb, const T* __restrict__ A_log, const T* __restrict__ dt_bias,
+                                  float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ kq, float* __restrict__ g,
+                                  float* __restrict__ beta, long tokens, int H, int KH, int D, int chan) {
+  const long wid = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= tokens * KH) return;
+  const long tok = wid / KH; const int kh = (int)(wid - tok * KH);
+  const T* qr = qkv + tok * ldq + kh * D; const T* kr = qkv + tok * ldq + koff + kh * D;
+  float qq = 0.f, kk = 0.f;
+  for (int i = lane; i < D; i += 32) { const float x = ldf(qr + i), y = ldf(kr + i); qq += x * x; kk += y * y; }
+  qq = warp_sum(qq); kk = warp_sum(kk);
+  const float qsc = (1.f / sqrtf((float)D)) / sqrtf(qq + 1e-6f), ksc = 1.f / sqrtf(kk + 1e-6f);
+  float dot = 0.f;
+  for (int i = lane; i < D; i += 32) {
+    const float x = ldf(qr + i) * qsc, y = ldf(kr + i) * ksc;
+    qn[(tok * KH + kh) * D + i] = x; kn[(tok * KH + kh) * D + i] = y; dot += x * y;
+  }
+  dot = warp_sum(dot);
+  if (lane == 0) kq[tok * KH + kh] = dot;
+  const int group = H / KH;
+  for (int hh = 0; hh < group; ++hh) {
+    const int h = kh * group + hh;
+    const float rate = expf(ldf(A_log + h));
+    if (chan) {
+      for (int i = lane; i < D; i += 32)
+        g[(tok * H + h) * D + i] = expf(-rate * softplusf_(ldf(a + tok * lda + h * D + i) + ldf(dt_bias + h * D + i)));
+    } else if (lane == 0) {
+      g[tok * H + h] = expf(-rate * softplusf_(ldf(a + tok * lda + h) + ldf(dt_bias + h)));
+    }
+    if (lane == 0) beta[tok * H + h] = sigmoidf_(ldf(bl + tok * ldb + h));
+  }
+}
+
 template <typename T, int DPT>
 __global__ void __launch_bounds__(256, DPT <= 16 ? 2 : 1)   // two blocks per SM where 128 registers hold the rows
-delta_scan_kernel(const T* __restrict__ qkv, long ldq, int koff, int voff, const T* __restrict__ a, long lda,
-                  const T* __restrict__ bl, long ldb, const T* __restrict__ A_log, const T* __restrict__ dt_bias,
+delta_scan_kernel(const T* __restrict__ qkv, long ldq, int voff, const float* __restrict__ qn, const float* __restrict__ kn,
+                  const float* __restrict__ kqs, const float* __restrict__ gs, const float* __restrict__ betas,
                   float* __restrict__ S, const int* __restrict__ seq_off, const int* __restrict__ slots,
                   const int* __restrict__ past, float* __restrict__ out, int H, int KH, int D, int V, int R, int VT, int chan) {
   extern __shared__ __align__(16) float sm[];
@@ -185,8 +257,6 @@ delta_scan_kernel(const T* __restrict__ qkv, long ldq, int koff, int voff, const
     const int i = r * DPT + d;
     s[d] = (past[b] > 0 && col_ok && i < D) ? Sg[(long)i * V + j] : 0.f;
   }
-  const float rate = expf(ldf(A_log + h));
-  const float qs = 1.f / sqrtf((float)D);
   for (int c0 = 0; c0 < n; c0 += CT) {
     const int ct = min(CT, n - c0);
     __syncthreads();
@@ -194,14 +264,10 @@ delta_scan_kernel(const T* __restrict__ qkv, long ldq, int koff, int voff, const
       const int t = e / Dr, i = e - t * Dr;
       const int pos = t * Dp + (i / DPT) * PS + (i % DPT);
       const long row = tok0 + c0 + t;
-      float kv = 0.f, qv = 0.f, gv = 1.f;
-      if (i < D) {
-        qv = ldf(qkv + row * ldq + kh * D + i);
-        kv = ldf(qkv + row * ldq + koff + kh * D + i);
-        if (chan) gv = expf(-rate * softplusf_(ldf(a + row * lda + h * D + i) + ldf(dt_bias + h * D + i)));
-      }
-      sk[pos] = kv; sq[pos] = qv;
-      if (chan) sg[pos] = gv;
+      const bool in = i < D;
+      sk[pos] = in ? kn[(row * KH + kh) * D + i] : 0.f;
+      sq[pos] = in ? qn[(row * KH + kh) * D + i] : 0.f;
+      if (chan) sg[pos] = in ? gs[(row * H + h) * D + i] : 1.f;
     }
     for (int e = tid; e < ct * VT; e += nth) {
       const int t = e / VT, c = e - t * VT;
@@ -209,27 +275,9 @@ delta_scan_kernel(const T* __restrict__ qkv, long ldq, int koff, int voff, const
     }
     for (int t = tid; t < ct; t += nth) {
       const long row = tok0 + c0 + t;
-      sbeta[t] = sigmoidf_(ldf(bl + row * ldb + h));
-      if (!chan) sg[t] = expf(-rate * softplusf_(ldf(a + row * lda + h) + ldf(dt_bias + h)));
-    }
-    __syncthreads();
-    // unit length per token: one warp per token
-    for (int t = tid >> 5; t < ct; t += nth >> 5) {
-      float kk = 0.f, qq = 0.f;
-      for (int i = tid & 31; i < Dr; i += 32) {
-        const int pos = t * Dp + (i / DPT) * PS + (i % DPT);
-        kk += sk[pos] * sk[pos]; qq += sq[pos] * sq[pos];
-      }
-      kk = warp_sum(kk); qq = warp_sum(qq);
-      const float ksc = 1.f / sqrtf(kk + 1e-6f), qsc = qs / sqrtf(qq + 1e-6f);
-      float kq = 0.f;
-      for (int i = tid & 31; i < Dr; i += 32) {
-        const int pos = t * Dp + (i / DPT) * PS + (i % DPT);
-        const float kx = sk[pos] * ksc, qx = sq[pos] * qsc;
-        sk[pos] = kx; sq[pos] = qx; kq += kx * qx;
-      }
-      kq = warp_sum(kq);
-      if ((tid & 31) == 0) skq[t] = kq;
+      sbeta[t] = betas[row * H + h];
+      skq[t] = kqs[row * KH + kh];
+      if (!chan) sg[t] = gs[row * H + h];
     }
     __syncthreads();
     // every thread walks the tokens (lanes of idle columns included: the shuffles below name the whole warp)
@@ -711,6 +759,15 @@ int lbs_slice_act(const void* in, long ldi, int idtype, void* out, long ldo, int
 int lbs_short_conv(const void* in, long ldi, const void* w, void* tail, const int* tok_seq, const int* seq_off, const int* slots,
                    const int* past, void* out, long ldo, long tokens, int B, int C, int taps, int dtype, cudaStream_t s) {
   if (tokens == 0) return 0;
+  const bool vec = dtype == 1 && C % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 && taps <= 8 && ((uintptr_t)in) % 16 == 0 &&
+                   ((uintptr_t)out) % 16 == 0 && ((uintptr_t)tail) % 16 == 0;
+  if (vec) {
+    short_conv_vec8_kernel<<<cdiv(tokens * (C / 8), 256), 256, 0, s>>>((const bf16*)in, ldi, (const bf16*)w, (const bf16*)tail, tok_seq,
+                                                                        seq_off, slots, past, (bf16*)out, ldo, tokens, C, taps);
+    if (taps > 1)
+      conv_tail_kernel<bf16><<<cdiv((long)B * C, 256), 256, 0, s>>>((const bf16*)in, ldi, (bf16*)tail, seq_off, slots, past, B, C, taps);
+    return ok();
+  }
   DISPATCH(dtype, {
     short_conv_kernel<T><<<cdiv(tokens * C, 256), 256, 0, s>>>((const T*)in, ldi, (const T*)w, (const T*)tail, tok_seq, seq_off, slots,
                                                                 past, (T*)out, ldo, tokens, C, taps);
@@ -720,11 +777,20 @@ int lbs_short_conv(const void* in, long ldi, const void* w, void* tail, const in
   return ok();
 }
 
+// work: fp32 scratch of at least tokens * (2*KH*D + KH + H + (chan ? H*D : H)) floats
 int lbs_delta_scan(const void* qkv, long ldq, int koff, int voff, const void* a, long lda, const void* bl, long ldb, const void* A_log,
-                   const void* dt_bias, float* S, const int* seq_off, const int* slots, const int* past, float* out, int B, int H,
-                   int KH, int D, int V, int chan, int dtype, cudaStream_t s) {
-  if (B == 0) return 0;
+                   const void* dt_bias, float* S, const int* seq_off, const int* slots, const int* past, float* out, float* work,
+                   long tokens, int B, int H, int KH, int D, int V, int chan, int dtype, cudaStream_t s) {
+  if (B == 0 || tokens == 0) return 0;
   if (D > 256 || H % KH != 0) return -1;
+  float* qn = work;
+  float* kn = qn + tokens * KH * D;
+  float* kq = kn + tokens * KH * D;
+  float* beta = kq + tokens * KH;
+  float* g = beta + tokens * H;
+  DISPATCH(dtype, delta_prep_kernel<T><<<cdiv(tokens * KH * 32, 256), 256, 0, s>>>((const T*)qkv, ldq, koff, (const T*)a, lda, (const T*)bl,
+                                                                                  ldb, (const T*)A_log, (const T*)dt_bias, qn, kn, kq, g,
+                                                                                  beta, tokens, H, KH, D, chan));
   const int dpt = D <= 32 ? 8 : (D <= 128 ? 16 : 32);  // rows per lane: 4 lanes per column up to D = 64, 8 lanes up to 256
   int R = 1;
   while (R * dpt < D) R <<= 1;                   // a power of two <= 8
@@ -737,9 +803,8 @@ int lbs_delta_scan(const void* qkv, long ldq, int koff, int voff, const void* a,
 #define DS(TT, P)                                                                                                              \
   {                                                                                                                            \
     if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<TT, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    delta_scan_kernel<TT, P><<<grid, threads, smem, s>>>((const TT*)qkv, ldq, koff, voff, (const TT*)a, lda, (const TT*)bl, ldb,   \
-                                                        (const TT*)A_log, (const TT*)dt_bias, S, seq_off, slots, past, out, H, KH, \
-                                                        D, V, R, VT, chan);                                                      \
+    delta_scan_kernel<TT, P><<<grid, threads, smem, s>>>((const TT*)qkv, ldq, voff, qn, kn, kq, g, beta, S, seq_off, slots, past, out, \
+                                                        H, KH, D, V, R, VT, chan);                                              \
   }
   if (dtype == 0) { if (dpt == 8) DS(float, 8) else if (dpt == 16) DS(float, 16) else DS(float, 32) }
   else { if (dpt == 8) DS(bf16, 8) else if (dpt == 16) DS(bf16, 16) else DS(bf16, 32) }

@@ -433,3 +433,21 @@ def test_slice_activation_between_column_slices(act):
     assert torch.allclose(wide[:, 32:96].float(), want[:, 16:80], atol=2e-2, rtol=2e-2)
     assert torch.allclose(odd[:, 5:42].float(), want[:, 3:40], atol=2e-2, rtol=2e-2)
     assert float(wide[:, :32].abs().max()) == 0 and float(wide[:, 96:].abs().max()) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("C,taps", [(64, 4), (24, 2), (20, 3)])
+def test_short_convolution_bf16_ragged_batch_on_the_gpu(C, taps):
+    g = torch.Generator().manual_seed(C + taps)
+    lens, past = [9, 1, 2, 14], [0, 5, 1, 0]
+    rb = RaggedBatch(lens, [3, 0, 2, 1], past, "cuda")
+    x = torch.randn(sum(lens), C, generator=g).to(torch.bfloat16)
+    w = torch.randn(C, taps, generator=g).to(torch.bfloat16)
+    tail = torch.randn(4, taps - 1, C, generator=g).to(torch.bfloat16)
+    out_gpu = torch.empty(sum(lens), C, dtype=torch.bfloat16, device="cuda")
+    tail_gpu = tail.cuda()
+    SF.short_conv(x.cuda(), w.cuda(), tail_gpu, rb, out_gpu)
+    out_cpu, tail_cpu = torch.empty(sum(lens), C, dtype=torch.bfloat16), tail.clone()
+    SF.short_conv(x, w, tail_cpu, RaggedBatch(lens, [3, 0, 2, 1], past, "cpu"), out_cpu)
+    assert torch.allclose(out_gpu.cpu().float(), out_cpu.float(), atol=2e-2, rtol=2e-2)
+    assert torch.equal(tail_gpu.cpu(), tail_cpu)
