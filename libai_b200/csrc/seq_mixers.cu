@@ -126,11 +126,12 @@ __global__ void short_conv_kernel(const T* __restrict__ in, long ldi, const T* _
 }
 
 // bf16 with 16-byte accesses: a thread owns 8 adjacent channels of one token (C, the row strides and the base addresses are
-// multiples of 8 elements; taps <= 8)
+// multiples of 8 elements); the 8·TAPS weights of its channels are contiguous and come in as TAPS 16-byte loads
+template <int TAPS>
 __global__ void short_conv_vec8_kernel(const __nv_bfloat16* __restrict__ in, long ldi, const __nv_bfloat16* __restrict__ w,
                                        const __nv_bfloat16* __restrict__ tail, const int* __restrict__ tok_seq,
                                        const int* __restrict__ seq_off, const int* __restrict__ slots, const int* __restrict__ past,
-                                       __nv_bfloat16* __restrict__ out, long ldo, long tokens, int C, int taps) {
+                                       __nv_bfloat16* __restrict__ out, long ldo, long tokens, int C) {
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const int C8 = C >> 3;
   if (idx >= tokens * C8) return;
@@ -138,18 +139,23 @@ __global__ void short_conv_vec8_kernel(const __nv_bfloat16* __restrict__ in, lon
   const int b = tok_seq[tok];
   const int t = (int)(tok - seq_off[b]);
   const bool has_past = past[b] > 0;
-  const __nv_bfloat16* tl = tail + (long)slots[b] * (taps - 1) * C;
+  const __nv_bfloat16* tl = tail + (long)slots[b] * (TAPS - 1) * C;
+  uint4 wraw[TAPS];
+#pragma unroll
+  for (int k = 0; k < TAPS; ++k) wraw[k] = reinterpret_cast<const uint4*>(w + (long)c * TAPS)[k];
+  const __nv_bfloat16* wv = reinterpret_cast<const __nv_bfloat16*>(wraw);      // wv[i * TAPS + j]: channel c + i, tap j
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-  for (int k = 0; k < taps; ++k) {
+#pragma unroll
+  for (int k = 0; k < TAPS; ++k) {
     const int tp = t - k;
     uint4 raw = make_uint4(0u, 0u, 0u, 0u);
     if (tp >= 0) raw = *reinterpret_cast<const uint4*>(in + (tok - k) * ldi + c);
-    else if (has_past) raw = *reinterpret_cast<const uint4*>(tl + (long)(taps - 1 + tp) * C + c);
+    else if (has_past) raw = *reinterpret_cast<const uint4*>(tl + (long)(TAPS - 1 + tp) * C + c);
     const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(&raw);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] += __bfloat162float(w[(long)(c + i) * taps + (taps - 1 - k)]) * __bfloat162float(x[i]);
+    for (int i = 0; i < 8; ++i) acc[i] += __bfloat162float(wv[i * TAPS + (TAPS - 1 - k)]) * __bfloat162float(x[i]);
   }
   uint4 res;
   __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
@@ -759,13 +765,16 @@ int lbs_slice_act(const void* in, long ldi, int idtype, void* out, long ldo, int
 int lbs_short_conv(const void* in, long ldi, const void* w, void* tail, const int* tok_seq, const int* seq_off, const int* slots,
                    const int* past, void* out, long ldo, long tokens, int B, int C, int taps, int dtype, cudaStream_t s) {
   if (tokens == 0) return 0;
-  const bool vec = dtype == 1 && C % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 && taps <= 8 && ((uintptr_t)in) % 16 == 0 &&
-                   ((uintptr_t)out) % 16 == 0 && ((uintptr_t)tail) % 16 == 0;
+  const bool vec = dtype == 1 && C % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 && taps >= 2 && taps <= 4 && ((uintptr_t)in) % 16 == 0 &&
+                   ((uintptr_t)out) % 16 == 0 && ((uintptr_t)tail) % 16 == 0 && ((uintptr_t)w) % 16 == 0;
   if (vec) {
-    short_conv_vec8_kernel<<<cdiv(tokens * (C / 8), 256), 256, 0, s>>>((const bf16*)in, ldi, (const bf16*)w, (const bf16*)tail, tok_seq,
-                                                                        seq_off, slots, past, (bf16*)out, ldo, tokens, C, taps);
-    if (taps > 1)
-      conv_tail_kernel<bf16><<<cdiv((long)B * C, 256), 256, 0, s>>>((const bf16*)in, ldi, (bf16*)tail, seq_off, slots, past, B, C, taps);
+    const int g = cdiv(tokens * (C / 8), 256);
+#define SC(TP)                                                                                                                   \
+  short_conv_vec8_kernel<TP><<<g, 256, 0, s>>>((const bf16*)in, ldi, (const bf16*)w, (const bf16*)tail, tok_seq, seq_off, slots, past, \
+                                               (bf16*)out, ldo, tokens, C)
+    if (taps == 2) SC(2); else if (taps == 3) SC(3); else SC(4);
+#undef SC
+    conv_tail_kernel<bf16><<<cdiv((long)B * C, 256), 256, 0, s>>>((const bf16*)in, ldi, (bf16*)tail, seq_off, slots, past, B, C, taps);
     return ok();
   }
   DISPATCH(dtype, {
