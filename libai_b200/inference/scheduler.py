@@ -8,6 +8,7 @@ logits processors / warpers (greedy when none samples).
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import torch
@@ -21,10 +22,42 @@ from libai_b200.inference.generator.generation_logits_processor import (
 from libai_b200.inference.ragged import RaggedBatch
 
 
+class _SingleTokenGraph:
+    """A captured CUDA graph of one single-token step for a fixed set of slots: tokens and past lengths live in persistent
+    device buffers that are refreshed before every replay; the logits come back in a persistent buffer."""
+
+    def __init__(self, model, slots, generation):
+        self.generation = generation
+        dev = model.head.device
+        self.rb = RaggedBatch.persistent_single(slots, dev)
+        self.tokens = torch.zeros(len(slots), dtype=torch.long, device=dev)
+        self.tokens_host = torch.zeros(len(slots), dtype=torch.long).pin_memory()
+        self.graph = torch.cuda.CUDAGraph()
+        self.logits = None
+        self.model = model
+
+    def capture(self):
+        torch.cuda.synchronize()
+        with torch.cuda.graph(self.graph):
+            self.logits = self.model.step_device(self.tokens, self.rb)
+
+    def run(self, tokens, past):
+        self.tokens_host.copy_(torch.tensor(tokens, dtype=torch.long))
+        self.tokens.copy_(self.tokens_host, non_blocking=True)
+        self.rb.set_past(past)
+        self.graph.replay()
+        return self.logits
+
+
 class RequestScheduler:
-    def __init__(self, model, max_tokens: Optional[int] = None):
+    MAX_GRAPHS = 8
+
+    def __init__(self, model, max_tokens: Optional[int] = None, cuda_graphs: Optional[bool] = None):
         self.model = model
         self.cache = model.state_cache()
+        # single-token steps of a batch that stays together replay from a CUDA graph (captured at the batch's second such step)
+        self.cuda_graphs = (os.environ.get("LIBAI_B200_DECODE_GRAPHS", "1") == "1") if cuda_graphs is None else cuda_graphs
+        self._graphs: Dict[tuple, object] = {}
         self.max_tokens = max_tokens          # advisory: the state of these models does not grow with the tokens held
         self.slot_of: Dict[Hashable, int] = {}
         self.device = model.head.device
@@ -42,6 +75,10 @@ class RequestScheduler:
                 self.slot_of[rid] = self.cache.allocate(1)[0]
         slots = [self.slot_of[rid] for rid, _, _ in entries]
         lens = [len(toks) for _, toks, _ in entries]
+        if self.cuda_graphs and self.device.type == "cuda" and all(n == 1 for n in lens) and hasattr(self.model, "step_device"):
+            logits = self._graphed_single_tokens(entries, slots)
+            if logits is not None:
+                return logits if any(want for _, _, want in entries) else None
         rb = RaggedBatch(lens, slots, [self.cache.length[s] for s in slots], self.device)
         flat = [t for _, toks, _ in entries for t in toks]
         rows = [rb.offsets[b] + w for b, (_, _, want) in enumerate(entries) for w in want]
@@ -49,6 +86,35 @@ class RequestScheduler:
         tokens, row_idx = packed[: len(flat)], packed[len(flat):]
         logits = self.model.step(tokens, rb, row_idx)
         return logits if rows else None
+
+    def _graphed_single_tokens(self, entries, slots):
+        """Replay (or capture) the graph of this slot set; ``None`` = run this step eagerly (first time the set is seen, or
+        capture is not possible).  Returns the wanted logits rows (a fresh tensor)."""
+        key = tuple(slots)
+        state = self._graphs.get(key)
+        if state is not None and state != "seen" and state.generation != self.cache.generation:
+            state = None                                        # the cache grew: its buffers moved
+        if state is None:
+            if len(self._graphs) >= self.MAX_GRAPHS:
+                self._graphs.pop(next(iter(self._graphs)))
+            self._graphs[key] = "seen"                          # the eager step warms everything a capture must not initialise
+            return None
+        past = [self.cache.length[s] for s in slots]
+        if state == "seen":
+            try:
+                state = _SingleTokenGraph(self.model, slots, self.cache.generation)
+                state.capture()
+            except Exception:                                   # capture refused (an operation that cannot be captured): stay eager
+                self.cuda_graphs = False
+                self._graphs.clear()
+                return None
+            self._graphs[key] = state
+        logits = state.run([toks[0] for _, toks, _ in entries], past)
+        self.cache.advance(slots, [1] * len(slots))
+        rows = [b for b, (_, _, want) in enumerate(entries) if want]
+        if len(rows) == len(entries):
+            return logits.clone()
+        return logits[torch.tensor(rows, dtype=torch.long, device=logits.device)] if rows else logits[:0]
 
     def finish(self, request_ids) -> None:
         for rid in request_ids:

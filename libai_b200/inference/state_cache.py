@@ -26,6 +26,7 @@ class SequenceStateCache:
         self._bufs: List[Dict[str, torch.Tensor]] = []
         self._free: List[int] = list(range(self.capacity - 1, -1, -1))
         self.length: Dict[int, int] = {}                      # live slot -> tokens folded into its state
+        self.generation = 0                                   # bumped when the buffers move (captured graphs are stale then)
 
     # ------------------------------------------------------------------ layout
     def register(self, kind: str, **shape) -> int:
@@ -81,3 +82,4 @@ class SequenceStateCache:
             self._bufs[i] = bigger
         self._free = list(range(new - 1, old - 1, -1)) + self._free
         self.capacity = new
+        self.generation += 1

@@ -195,8 +195,16 @@ class BumodraForCausalLM(nn.Module, Generator):
         step's slots.  Returns fp32 logits of the packed rows ``logits_rows`` (default: all), ``[rows, vocab]``."""
         cache = self.state_cache()
         tokens = tokens.to(self.head.device, torch.long).contiguous()
-        x = self.model(tokens, rb, cache, self._handles, tap=tap)
+        logits = self.step_device(tokens, rb, logits_rows, tap=tap)
         cache.advance(rb.slot_list, rb.lens)
+        return logits
+
+    @torch.no_grad()
+    def step_device(self, tokens, rb: RaggedBatch, logits_rows=None, tap=None):
+        """The device work of :meth:`step` alone (kernel launches only, no host-side bookkeeping): this is what a CUDA graph of a
+        single-token step captures."""
+        cache = self.state_cache()
+        x = self.model(tokens, rb, cache, self._handles, tap=tap)
         if logits_rows is not None:
             x = x.index_select(0, logits_rows)
         h = torch.empty(x.shape, dtype=self.head.dtype, device=x.device)

@@ -63,9 +63,8 @@ def linear_accumulate(x32, a, w):
     if (a.is_cuda and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and use_native(a) and a.stride(-1) == 1
             and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and w.shape[0] % 8 == 0 and x32.stride(0) % 4 == 0
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and a.shape[0] > 0):
-        count_launch()
-        load_ext().gemm(a, w, 0, None, x32, True, torch.float32)
-        return x32
+        if _tcgen05_gemm(a, w, x32, True, torch.float32) is not None:
+            return x32
     if a.dtype == torch.float32:
         return x32.addmm_(a, w.t())
     return x32.add_(F.linear(a, w).float())
@@ -249,9 +248,32 @@ def linear(a, w):
     if (a.is_cuda and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and use_native(a) and a.dim() == 2
             and a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.shape[1] % 8 == 0 and w.is_contiguous()
             and w.shape[0] % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and a.shape[0] > 0):
-        count_launch()
-        return load_ext().gemm(a, w, 0, None, None, False, torch.bfloat16)
+        y = _tcgen05_gemm(a, w, None, False, torch.bfloat16)
+        if y is not None:
+            return y
     return F.linear(a, w)
+
+
+_GEMM_REFUSED = set()
+
+
+def _tcgen05_gemm(a, w, out, accumulate, out_dtype):
+    """The framework's GEMM; a shape it refuses (the launcher returns an error code before anything runs) is remembered and
+    sent to the vendor product from then on — ``None`` tells the caller to do so."""
+    from . import load_ext
+
+    key = (a.shape[0] > 1, a.shape[1], w.shape[0], a.stride(0), accumulate)
+    if key in _GEMM_REFUSED:
+        return None
+    try:
+        y = load_ext().gemm(a, w, 0, None, out, accumulate, out_dtype)
+    except RuntimeError as e:
+        if "failed with code -" not in str(e):          # a CUDA error, not a refusal by the launcher's shape checks
+            raise
+        _GEMM_REFUSED.add(key)
+        return None
+    count_launch()
+    return y
 
 
 def fuse_rows(named, align: int = 8):

@@ -451,3 +451,31 @@ def test_short_convolution_bf16_ragged_batch_on_the_gpu(C, taps):
     SF.short_conv(x, w, tail_cpu, RaggedBatch(lens, [3, 0, 2, 1], past, "cpu"), out_cpu)
     assert torch.allclose(out_gpu.cpu().float(), out_cpu.float(), atol=2e-2, rtol=2e-2)
     assert torch.equal(tail_gpu.cpu(), tail_cpu)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_single_token_steps_from_cuda_graphs_equal_eager_steps(tmp_path, dtype):
+    cfg = mixed_cfg(width=32)
+    model, w = make(tmp_path, cfg, "cuda", dtype=dtype)
+    prompts = [tokens(n, seed=60 + n) for n in (9, 4, 13)]
+    tails = [tokens(14, seed=70), tokens(6, seed=71), tokens(14, seed=72)]        # the second request leaves the batch early
+
+    def run(graphs):
+        sched = RequestScheduler(model, cuda_graphs=graphs)
+        out = [sched.step([(i, p, [len(p) - 1]) for i, p in enumerate(prompts)])]
+        for t in range(14):
+            live = [i for i in range(3) if t < len(tails[i])]
+            out.append(sched.step([(i, [tails[i][t]], [0]) for i in live]))
+            sched.finish([i for i in live if t + 1 == len(tails[i])])
+        assert sched.cache.live() == 0
+        return torch.cat(out), sched
+
+    eager, _ = run(False)
+    graphed, sched = run(True)
+    assert any(v != "seen" for v in sched._graphs.values())                        # graphs were captured and replayed
+    assert torch.allclose(eager, graphed, atol=1e-5 if dtype == torch.float32 else 2e-2)
+    if dtype == torch.float32:
+        want = O.model_logits(cfg, w, prompts[0] + tails[0])[len(prompts[0]) - 1:]
+        got = torch.stack([graphed[0]] + [graphed[3 + (3 * t if t < 6 else 18 + 2 * (t - 6))] for t in range(14)])
+        assert rel_err(got, want) < 1e-4
