@@ -46,23 +46,6 @@ class RaggedBatch:
         self.tok_seq = packed[3 * B + 1:]
         self._ext: Dict[int, WindowExt] = {}
         self._tiles: Dict[int, tuple] = {}
-        self._past_host = None
-
-    @classmethod
-    def persistent_single(cls, slots: Sequence[int], device) -> "RaggedBatch":
-        """One token per sequence with the descriptor in a device buffer that stays where it is: a captured CUDA graph of
-        the step keeps reading it, :meth:`set_past` refreshes the only part that changes between steps."""
-        rb = cls([1] * len(slots), slots, [0] * len(slots), device)
-        rb._past_host = torch.zeros(len(slots), dtype=torch.int32).pin_memory() if rb.device.type == "cuda" else None
-        return rb
-
-    def set_past(self, past: Sequence[int]) -> None:
-        self.past_list = list(past)
-        if self._past_host is not None:
-            self._past_host.copy_(torch.tensor(self.past_list, dtype=torch.int32))
-            self.past.copy_(self._past_host, non_blocking=True)
-        else:
-            self.past.copy_(torch.tensor(self.past_list, dtype=torch.int32))
 
     def ext(self, window: int) -> WindowExt:
         if window not in self._ext:

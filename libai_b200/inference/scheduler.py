@@ -29,9 +29,9 @@ class _SingleTokenGraph:
     def __init__(self, model, slots, generation):
         self.generation = generation
         dev = model.head.device
-        self.rb = RaggedBatch.persistent_single(slots, dev)
-        self.tokens = torch.zeros(len(slots), dtype=torch.long, device=dev)
-        self.tokens_host = torch.zeros(len(slots), dtype=torch.long).pin_memory()
+        self.n = len(slots)
+        self.rb = RaggedBatch(self.n * [1], slots, self.n * [0], dev)
+        self.io = torch.zeros(2 * self.n, dtype=torch.long, device=dev)       # [tokens | past lengths], refreshed per step
         self.graph = torch.cuda.CUDAGraph()
         self.logits = None
         self.model = model
@@ -39,12 +39,12 @@ class _SingleTokenGraph:
     def capture(self):
         torch.cuda.synchronize()
         with torch.cuda.graph(self.graph):
-            self.logits = self.model.step_device(self.tokens, self.rb)
+            self.rb.past.copy_(self.io[self.n:])                              # int64 → the descriptor's int32, on the device
+            self.logits = self.model.step_device(self.io[: self.n], self.rb)
 
     def run(self, tokens, past):
-        self.tokens_host.copy_(torch.tensor(tokens, dtype=torch.long))
-        self.tokens.copy_(self.tokens_host, non_blocking=True)
-        self.rb.set_past(past)
+        # one copy from a fresh pageable tensor: the host may not touch a staging buffer that a queued copy still reads
+        self.io.copy_(torch.tensor(list(tokens) + list(past), dtype=torch.long))
         self.graph.replay()
         return self.logits
 
