@@ -1,0 +1,661 @@
+// Kernels of decoders whose attention layers keep keys and values in per-sequence rings: Dynamic-Tanh norms on an fp32
+// residual stream, query/key preparation (whole-projection or per-head RMS norms, rotary positions with per-dimension
+// frequencies), ring / kept-first-token caches, grouped-query attention under a position mask (chunks, or a sliding
+// window that also keeps the first tokens of the sequence) for prompts and for single-token steps, and a
+// mixture-of-experts feed-forward (sigmoid router with top-k choice, gated experts).
+//
+// Conventions (the same ragged-batch descriptor as seq_mixers.cu).  A step carries B sequences; sequence b brings
+// n_b = seq_off[b+1]-seq_off[b] new tokens packed at rows seq_off[b].. of every activation matrix, has past[b] tokens
+// already in its state, which lives in slot slots[b].  The token at packed row r of sequence b has position
+// past[b] + r - seq_off[b].  Activations are `T` (float or bf16, `dtype` 0 / 1); softmax, norms, the router and the
+// residual stream are fp32 in both.  Built WITHOUT fast-math: the fp32 mode is exact to rounding.
+//
+// Key/value rows.  A cache row is [G*D keys | G*V values] (C numbers) of one position.  Position p of a sequence
+// lives at ring[slot][p % L]; positions below `nfirst` are also kept in first[slot][p] and never leave.  A prompt step
+// reads its keys from an "ext" matrix: per sequence the rows [kept-first positions that are older than the contiguous
+// part | cached positions cstart..past-1 | the step's own rows], ext_off[b] giving the first row, nsink[b] the number
+// of rows of the first part and cstart[b] the position of the first row of the contiguous part.  A single-token step
+// reads ring and `first` directly (its own row is written before).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+  return v;
+}
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+
+// dot product of a weight row with a vector staged in shared memory as fp32; the lanes of one warp share the row.
+template <typename T>
+__device__ __forceinline__ float warp_dot(const T* __restrict__ w, const float* __restrict__ xs, int n, int lane);
+template <>
+__device__ __forceinline__ float warp_dot<float>(const float* __restrict__ w, const float* __restrict__ xs, int n, int lane) {
+  float acc = 0.f;
+  if ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+    for (int i = lane * 4; i < n; i += 128) {
+      const float4 v = *reinterpret_cast<const float4*>(w + i);
+      acc += v.x * xs[i] + v.y * xs[i + 1] + v.z * xs[i + 2] + v.w * xs[i + 3];
+    }
+  } else {
+    for (int i = lane; i < n; i += 32) acc += w[i] * xs[i];
+  }
+  return warp_sum(acc);
+}
+template <>
+__device__ __forceinline__ float warp_dot<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w, const float* __restrict__ xs, int n,
+                                                         int lane) {
+  float acc = 0.f;
+  if ((n & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+    for (int i = lane * 8; i < n; i += 256) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(w + i);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(p[j]);
+        acc += f.x * xs[i + 2 * j] + f.y * xs[i + 2 * j + 1];
+      }
+    }
+  } else {
+    for (int i = lane; i < n; i += 32) acc += __bfloat162float(w[i]) * xs[i];
+  }
+  return warp_sum(acc);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Embedding lookup with a constant factor into the fp32 stream: x[r] = table[ids[r]] * scale.
+// ------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_scale_kernel(const T* __restrict__ table, const int64_t* __restrict__ ids, float scale, float* __restrict__ x,
+                                   int n) {
+  const long r = blockIdx.x;
+  const T* src = table + ids[r] * (long)n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) x[r * n + i] = ldf(src + i) * scale;
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Dynamic Tanh norm, dyt(v) = tanh(alpha v) w + b (elementwise; no statistics), fused around the residual sum:
+//   x[r] += dyt_post(y[r])      when y is given (y: rows of a sublayer's output, or — `pos` given — the weighted sum
+//                               over `top` rows of a sorted expert output, y[pos[r,k]] * cw[r,k])
+//   h[r]  = dyt_next(x[r])      when h is given
+// x is the fp32 residual stream and is updated in place.
+// ------------------------------------------------------------------------------------------------------------------
+template <typename T, typename Ty>
+__global__ void dyt_residual_kernel(float* __restrict__ x, const Ty* __restrict__ y, long ldy, const int* __restrict__ pos,
+                                    const float* __restrict__ cw, int top, const T* __restrict__ pw, const T* __restrict__ pb,
+                                    const T* __restrict__ palpha, const T* __restrict__ nw, const T* __restrict__ nb,
+                                    const T* __restrict__ nalpha, T* __restrict__ h, long ldh, int n) {
+  const long r = blockIdx.x;
+  const float pa = y ? ldf(palpha) : 0.f, na = h ? ldf(nalpha) : 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = x[r * n + i];
+    if (y) {
+      float yv;
+      if (pos) {
+        yv = 0.f;
+        for (int k = 0; k < top; ++k) yv += cw[r * top + k] * ldf(y + (long)pos[r * top + k] * ldy + i);
+      } else {
+        yv = ldf(y + r * ldy + i);
+      }
+      v += tanhf(pa * yv) * ldf(pw + i) + ldf(pb + i);
+      x[r * n + i] = v;
+    }
+    if (h) stf(h + r * ldh + i, tanhf(na * v) * ldf(nw + i) + ldf(nb + i));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Elementwise activations between column slices: out = act(in), or — gated — out = act(in[:, :n]) * in[:, n:2n].
+// ------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float act_apply(float v, int act) {
+  switch (act) {
+    case 1: return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));                                   // gelu (erf)
+    case 2: return v * sigmoidf_(v);                                                                          // silu
+    case 3: return 0.5f * v * (1.f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v)));          // gelu (tanh)
+    case 4: { const float r = fmaxf(v, 0.f); return r * r; }                                                 // relu squared
+    default: return v;
+  }
+}
+template <typename T>
+__global__ void act_rows_kernel(const T* __restrict__ in, long ldi, T* __restrict__ out, long ldo, long rows, int n, int act,
+                                int gated) {
+  const long total = rows * n;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / n; const int c = (int)(i - r * n);
+    float v = act_apply(ldf(in + r * ldi + c), act);
+    if (gated) v *= ldf(in + r * ldi + n + c);
+    stf(out + r * ldo + c, v);
+  }
+}
+
+__global__ void softcap_kernel(float* __restrict__ l, float cap, long total) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x)
+    l[i] = cap * tanhf(l[i] / cap);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Query / key preparation, in place, one block per token:
+//   full_norm : q <- q / rms(q over all H*D) * qw, the same for k over all G*D (before rotation)
+//   rotation  : the first `rot` channels of every head, channel i paired with i + rot/2, angle = position * freq[i];
+//               cos and sin are multiplied by `mscale`
+//   unit_norm : every head divided by its root mean square over D (after rotation, no weight)
+// k may be absent (a layer that reads another layer's keys).
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int QK_MAXD = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+qk_prepare_kernel(T* __restrict__ q, long ldq, T* __restrict__ k, long ldk, const T* __restrict__ qw, const T* __restrict__ kw,
+                  const float* __restrict__ freq, float mscale, int rot, int H, int G, int D, float eps, int full_norm,
+                  int unit_norm, const int* __restrict__ tok_seq, const int* __restrict__ seq_off, const int* __restrict__ past) {
+  extern __shared__ float sm[];
+  float* cs = sm; float* sn = sm + rot / 2; float* red = sm + rot;
+  const long tok = blockIdx.x;
+  const int b = tok_seq[tok];
+  const int pos = past[b] + (int)(tok - seq_off[b]);
+  const int half = rot / 2;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float s, c;
+    sincosf((float)pos * freq[i], &s, &c);
+    cs[i] = c * mscale; sn[i] = s * mscale;
+  }
+  T* qr = q + tok * ldq;
+  T* kr = k ? k + tok * ldk : nullptr;
+  float rq = 1.f, rk = 1.f;
+  if (full_norm) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < H * D; i += blockDim.x) { const float v = ldf(qr + i); s += v * v; }
+    rq = 1.f / sqrtf(block_sum(s, red) / (float)(H * D) + eps);
+    if (kr) {
+      s = 0.f;
+      for (int i = threadIdx.x; i < G * D; i += blockDim.x) { const float v = ldf(kr + i); s += v * v; }
+      rk = 1.f / sqrtf(block_sum(s, red) / (float)(G * D) + eps);
+    }
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int heads = H + (kr ? G : 0);
+  for (int hh = warp; hh < heads; hh += nw) {
+    const bool isq = hh < H;
+    T* p = isq ? qr + hh * D : kr + (hh - H) * D;
+    const T* w = full_norm ? (isq ? qw + hh * D : kw + (hh - H) * D) : nullptr;
+    const float sc = isq ? rq : rk;
+    float ru[QK_MAXD / 64], rv[QK_MAXD / 64], rp[QK_MAXD / 32];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < QK_MAXD / 64; ++j) {
+      const int i = lane + 32 * j;
+      if (i < half) {
+        float u = ldf(p + i) * sc, v = ldf(p + i + half) * sc;
+        if (w) { u *= ldf(w + i); v *= ldf(w + i + half); }
+        ru[j] = u * cs[i] - v * sn[i];
+        rv[j] = v * cs[i] + u * sn[i];
+        ss += ru[j] * ru[j] + rv[j] * rv[j];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < QK_MAXD / 32; ++j) {
+      const int i = rot + lane + 32 * j;
+      if (i < D) {
+        float u = ldf(p + i) * sc;
+        if (w) u *= ldf(w + i);
+        rp[j] = u;
+        ss += u * u;
+      }
+    }
+    float un = 1.f;
+    if (unit_norm) un = 1.f / sqrtf(warp_sum(ss) / (float)D + eps);
+#pragma unroll
+    for (int j = 0; j < QK_MAXD / 64; ++j) {
+      const int i = lane + 32 * j;
+      if (i < half) { stf(p + i, ru[j] * un); stf(p + i + half, rv[j] * un); }
+    }
+#pragma unroll
+    for (int j = 0; j < QK_MAXD / 32; ++j) {
+      const int i = rot + lane + 32 * j;
+      if (i < D) stf(p + i, rp[j] * un);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Cache rows.  kv_write: the step's key rows (G*D) and value rows (G*V) go to ring[slot][pos % L] (only the last L of a
+// sequence's new tokens) and, for pos < nfirst, to first[slot][pos].  kv_gather: builds the ext matrix of a prompt step.
+// ------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void kv_write_kernel(T* __restrict__ ring, T* __restrict__ first, const T* __restrict__ knew, const T* __restrict__ vnew,
+                                long ldn, const int* __restrict__ tok_seq, const int* __restrict__ seq_off,
+                                const int* __restrict__ slots, const int* __restrict__ past, int KC, int VC, int L, int nfirst) {
+  const long tok = blockIdx.x;
+  const int b = tok_seq[tok];
+  const int t = (int)(tok - seq_off[b]), n = seq_off[b + 1] - seq_off[b];
+  const int pos = past[b] + t, C = KC + VC;
+  const long slot = slots[b];
+  if (n - t <= L) {
+    T* dst = ring + (slot * L + pos % L) * C;
+    for (int i = threadIdx.x; i < KC; i += blockDim.x) dst[i] = knew[tok * ldn + i];
+    for (int i = threadIdx.x; i < VC; i += blockDim.x) dst[KC + i] = vnew[tok * ldn + i];
+  }
+  if (pos < nfirst) {
+    T* dst = first + (slot * nfirst + pos) * C;
+    for (int i = threadIdx.x; i < KC; i += blockDim.x) dst[i] = knew[tok * ldn + i];
+    for (int i = threadIdx.x; i < VC; i += blockDim.x) dst[KC + i] = vnew[tok * ldn + i];
+  }
+}
+
+template <typename T>
+__global__ void kv_gather_kernel(const T* __restrict__ ring, const T* __restrict__ first, const T* __restrict__ knew,
+                                 const T* __restrict__ vnew, long ldn, const int* __restrict__ ext_seq, const int* __restrict__ ext_off,
+                                 const int* __restrict__ nsink, const int* __restrict__ cstart, const int* __restrict__ seq_off,
+                                 const int* __restrict__ slots, const int* __restrict__ past, T* __restrict__ ext, int KC, int VC, int L,
+                                 int nfirst) {
+  const long r = blockIdx.x;
+  const int b = ext_seq[r], C = KC + VC;
+  const int rel = (int)(r - ext_off[b]), ns = nsink[b], cached = past[b] - cstart[b];
+  const long slot = slots[b];
+  T* dst = ext + r * C;
+  if (rel < ns + cached) {
+    const T* src = rel < ns ? first + (slot * nfirst + rel) * C : ring + (slot * L + (cstart[b] + rel - ns) % L) * C;
+    for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = src[i];
+  } else {
+    const long tok = seq_off[b] + (rel - ns - cached);
+    for (int i = threadIdx.x; i < KC; i += blockDim.x) dst[i] = knew[tok * ldn + i];
+    for (int i = threadIdx.x; i < VC; i += blockDim.x) dst[KC + i] = vnew[tok * ldn + i];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Grouped-query attention under a position mask.  The query at position i sees position j <= i when
+//   chunk  > 0 : j >= floor(i / chunk) * chunk                                    (chunks counted from position 0)
+//   window > 0 : j > i - window, or j < keep                                      (sliding window + kept first tokens)
+// (neither: every j <= i).  Query head h reads key/value head h / (H/G).  One warp per (token, head): lanes take keys
+// for the scores and value channels for the output; softmax in fp32, streamed 32 keys at a time.  The head's output is
+// multiplied by sigmoid(gate[tok, h]) when a gate is given.  Keys come from the ext matrix (kbase/vbase with row stride
+// ldkv) or, when `ring` is given, from ring / first (single-token steps).
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int ATT_MAXV = 8;    // value channels per lane: V <= 256
+
+struct KvSource {
+  const void* kbase; const void* vbase; long ldkv;            // ext mode
+  const void* ring; const void* first; int L, nfirst, C, KC;  // ring mode
+  const int* ext_off; const int* nsink; const int* cstart; const int* slots;
+};
+
+template <typename T>
+__device__ __forceinline__ void kv_row(const KvSource& s, int b, int pos, int g, int D, int V, const T*& kp, const T*& vp) {
+  if (s.ring) {
+    const long slot = s.slots[b];
+    const T* base = pos < s.nfirst ? (const T*)s.first + (slot * s.nfirst + pos) * s.C : (const T*)s.ring + (slot * s.L + pos % s.L) * s.C;
+    kp = base + g * D; vp = base + s.KC + g * V;
+  } else {
+    const int cs = s.cstart[b];
+    const long row = (long)s.ext_off[b] + (pos < cs ? pos : s.nsink[b] + pos - cs);
+    kp = (const T*)s.kbase + row * s.ldkv + g * D; vp = (const T*)s.vbase + row * s.ldkv + g * V;
+  }
+}
+
+template <typename T>
+__global__ void masked_attention_kernel(const T* __restrict__ q, long ldq, KvSource src, const T* __restrict__ gate, long ldg,
+                                        const int* __restrict__ tok_seq, const int* __restrict__ seq_off, const int* __restrict__ past,
+                                        T* __restrict__ y, long ldy, long tokens, int H, int G, int D, int V, int window, int chunk,
+                                        int keep, float scale) {
+  extern __shared__ float sm[];
+  const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long wid = (long)blockIdx.x * (blockDim.x >> 5) + wib;
+  if (wid >= tokens * H) return;                 // no block-level sync below
+  const long tok = wid / H; const int h = (int)(wid - tok * H);
+  const int g = h / (H / G);
+  const int b = tok_seq[tok];
+  const int pi = past[b] + (int)(tok - seq_off[b]);
+  int lo = 0;
+  if (chunk > 0) lo = (pi / chunk) * chunk; else if (window > 0) lo = max(0, pi - window + 1);
+  const int nA = (chunk > 0) ? 0 : min(keep, lo);
+  const int total = nA + (pi - lo + 1);
+  float* qs = sm + wib * D;
+  for (int i = lane; i < D; i += 32) qs[i] = ldf(q + tok * ldq + h * D + i) * scale;
+  __syncwarp();
+  float m = -INFINITY, l = 0.f, acc[ATT_MAXV];
+#pragma unroll
+  for (int i = 0; i < ATT_MAXV; ++i) acc[i] = 0.f;
+  for (int e = 0; e < total; e += 32) {
+    const int mine = e + lane;
+    float sc = -INFINITY;
+    const T* kp = nullptr; const T* vp = nullptr;
+    if (mine < total) {
+      kv_row<T>(src, b, mine < nA ? mine : lo + mine - nA, g, D, V, kp, vp);
+      float d = 0.f;
+      for (int i = 0; i < D; ++i) d += qs[i] * ldf(kp + i);
+      sc = d;
+    }
+    const float mn = fmaxf(m, warp_max(sc));
+    const float corr = expf(m - mn);             // m = -inf on the first block: exp(-inf) = 0
+    const float p = mine < total ? expf(sc - mn) : 0.f;
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int i = 0; i < ATT_MAXV; ++i) acc[i] *= corr;
+    const int cnt = min(32, total - e);
+    for (int kk = 0; kk < cnt; ++kk) {
+      const float pk = __shfl_sync(0xffffffffu, p, kk);
+      const T* vr = (const T*)__shfl_sync(0xffffffffu, (unsigned long long)vp, kk);
+#pragma unroll
+      for (int i = 0; i < ATT_MAXV; ++i) { const int c = lane + 32 * i; if (c < V) acc[i] += pk * ldf(vr + c); }
+    }
+    m = mn;
+  }
+  const float gt = gate ? sigmoidf_(ldf(gate + tok * ldg + h)) : 1.f;
+  const float inv = gt / l;
+#pragma unroll
+  for (int i = 0; i < ATT_MAXV; ++i) { const int c = lane + 32 * i; if (c < V) stf(y + tok * ldy + h * V + c, acc[i] * inv); }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Mixture of experts.
+//   moe_route   : z = W_r h in fp32, s = sigmoid(z), the `top` largest (ties: the lower index), weights s / (sum + 1e-20)
+//                 * rscale; optionally counts the tokens of every expert.
+//   pair kernels: few tokens (single-token steps): every (token, chosen expert) pair reads its expert's matrices —
+//                 a = act(W_gate h) * (W_up h), then out[t] = sum_k weight_k W_down,k a_k in fp32.
+//   sort kernels: many tokens: rows are copied into a matrix sorted by expert (offsets from the counts), the experts
+//                 run as dense products on their row ranges, and the fused residual kernel gathers the weighted sum.
+// Expert matrices are stacked: wgu [E, 2*ff, n] (gate rows, then up rows), wd [E, n, ff].
+// ------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ wr, int E, int n, int top, float rscale,
+                                 int* __restrict__ idx, float* __restrict__ wts, int* __restrict__ counts, long tokens) {
+  extern __shared__ float sm[];
+  const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const long tok = (long)blockIdx.x * nw + wib;
+  float* hs = sm + (long)wib * (n + E);
+  float* sc = hs + n;
+  if (tok >= tokens) return;                     // warps are independent below
+  for (int i = lane; i < n; i += 32) hs[i] = ldf(h + tok * ldh + i);
+  __syncwarp();
+  for (int e = 0; e < E; ++e) {
+    const float z = warp_dot<T>(wr + (long)e * n, hs, n, lane);
+    if (lane == 0) sc[e] = sigmoidf_(z);
+  }
+  __syncwarp();
+  float sum = 0.f, mine_w = 0.f; int mine_e = 0;
+  for (int k = 0; k < top; ++k) {
+    float best = -1.f; int be = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) { const float v = sc[e]; if (v > best) { best = v; be = e; } }
+#pragma unroll
+    for (int mk = 16; mk > 0; mk >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, mk);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, mk);
+      if (ov > best || (ov == best && oe < be)) { best = ov; be = oe; }
+    }
+    sum += best;
+    if (lane == k % 32) { mine_w = best; mine_e = be; }
+    if (lane == 0) sc[be] = -2.f;
+    __syncwarp();
+    if (k % 32 == 31 || k == top - 1) {          // flush up to 32 choices held one per lane
+      const int k0 = k - (k % 32);
+      if (lane <= k - k0) { idx[tok * top + k0 + lane] = mine_e; wts[tok * top + k0 + lane] = mine_w; }
+    }
+  }
+  __syncwarp();
+  const float inv = rscale / (sum + 1e-20f);
+  for (int k = lane; k < top; k += 32) {
+    wts[tok * top + k] *= inv;
+    if (counts) atomicAdd(counts + idx[tok * top + k], 1);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_pair_gateup_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ wgu, const int* __restrict__ idx, T* __restrict__ a,
+                       int ff, int n, int top, int act) {
+  extern __shared__ float sm[];
+  const long pair = blockIdx.x;
+  const long tok = pair / top;
+  const int e = idx[pair];
+  for (int i = threadIdx.x; i < n; i += blockDim.x) sm[i] = ldf(h + tok * ldh + i);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int per = (ff + gridDim.y - 1) / gridDim.y;
+  const int f0 = blockIdx.y * per, f1 = min(ff, f0 + per);
+  const T* wg = wgu + (long)e * 2 * ff * n;
+  for (int f = f0 + warp; f < f1; f += nw) {
+    const float gv = warp_dot<T>(wg + (long)f * n, sm, n, lane);
+    const float uv = warp_dot<T>(wg + (long)(ff + f) * n, sm, n, lane);
+    if (lane == 0) stf(a + pair * ff + f, act_apply(gv, act) * uv);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_pair_down_kernel(const T* __restrict__ a, const T* __restrict__ wd, const int* __restrict__ idx, const float* __restrict__ wts,
+                     float* __restrict__ out, int ff, int n, int top) {
+  extern __shared__ float sm[];
+  const long tok = blockIdx.x;
+  for (int i = threadIdx.x; i < top * ff; i += blockDim.x) sm[i] = ldf(a + tok * top * ff + i);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int per = (n + gridDim.y - 1) / gridDim.y;
+  const int c0 = blockIdx.y * per, c1 = min(n, c0 + per);
+  for (int c = c0 + warp; c < c1; c += nw) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int e = idx[tok * top + k];
+      acc += wts[tok * top + k] * warp_dot<T>(wd + ((long)e * n + c) * ff, sm + k * ff, ff, lane);
+    }
+    if (lane == 0) out[tok * n + c] = acc;
+  }
+}
+
+// offsets[e] = first sorted row of expert e (offsets[E] = all pairs); the per-expert cursors start at zero
+__global__ void moe_offsets_kernel(const int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ cursor, int E) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) { offsets[e] = at; at += counts[e]; cursor[e] = 0; }
+    offsets[E] = at;
+  }
+}
+
+template <typename T>
+__global__ void moe_scatter_kernel(const T* __restrict__ h, long ldh, const int* __restrict__ idx, const int* __restrict__ offsets,
+                                   int* __restrict__ cursor, int* __restrict__ pos, T* __restrict__ xs, int n, int top) {
+  __shared__ int where;
+  const long pair = blockIdx.x;
+  if (threadIdx.x == 0) {
+    const int e = idx[pair];
+    where = offsets[e] + atomicAdd(cursor + e, 1);
+    pos[pair] = where;
+  }
+  __syncthreads();
+  const T* src = h + (pair / top) * ldh;
+  T* dst = xs + (long)where * n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+}
+
+}  // namespace
+
+// ====================================================================================================================
+// launchers (C ABI; return 0, a CUDA error code, or -1 for sizes a kernel is not built for)
+// ====================================================================================================================
+#define LAUNCH_END() do { cudaError_t e_ = cudaGetLastError(); return e_ == cudaSuccess ? 0 : (int)e_; } while (0)
+typedef __nv_bfloat16 bf16;
+
+extern "C" {
+
+int lbk_embed_scale(const void* table, const int64_t* ids, float scale, float* x, long rows, int n, int dtype, cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (dtype) embed_scale_kernel<bf16><<<(unsigned)rows, 256, 0, s>>>((const bf16*)table, ids, scale, x, n);
+  else embed_scale_kernel<float><<<(unsigned)rows, 256, 0, s>>>((const float*)table, ids, scale, x, n);
+  LAUNCH_END();
+}
+
+int lbk_dyt_residual(float* x, const void* y, long ldy, int ydtype, const int* pos, const float* cw, int top, const void* pw,
+                     const void* pb, const void* palpha, const void* nw, const void* nb, const void* nalpha, void* h, long ldh,
+                     long rows, int n, int dtype, cudaStream_t s) {
+  if (rows == 0) return 0;
+  const int th = n >= 1024 ? 256 : 128;
+#define DYT(T, Ty) dyt_residual_kernel<T, Ty><<<(unsigned)rows, th, 0, s>>>(x, (const Ty*)y, ldy, pos, cw, top, (const T*)pw, \
+    (const T*)pb, (const T*)palpha, (const T*)nw, (const T*)nb, (const T*)nalpha, (T*)h, ldh, n)
+  if (dtype) { if (ydtype) DYT(bf16, bf16); else DYT(bf16, float); }
+  else { if (ydtype) return -1; DYT(float, float); }
+#undef DYT
+  LAUNCH_END();
+}
+
+int lbk_act_rows(const void* in, long ldi, void* out, long ldo, long rows, int n, int act, int gated, int dtype, cudaStream_t s) {
+  if (rows == 0 || n == 0) return 0;
+  const long total = rows * n;
+  const unsigned grid = (unsigned)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+  if (dtype) act_rows_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)in, ldi, (bf16*)out, ldo, rows, n, act, gated);
+  else act_rows_kernel<float><<<grid, 256, 0, s>>>((const float*)in, ldi, (float*)out, ldo, rows, n, act, gated);
+  LAUNCH_END();
+}
+
+int lbk_softcap(float* l, float cap, long total, cudaStream_t s) {
+  if (total == 0) return 0;
+  const unsigned grid = (unsigned)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+  softcap_kernel<<<grid, 256, 0, s>>>(l, cap, total);
+  LAUNCH_END();
+}
+
+int lbk_qk_prepare(void* q, long ldq, void* k, long ldk, const void* qw, const void* kw, const float* freq, float mscale, int rot,
+                   int H, int G, int D, float eps, int full_norm, int unit_norm, const int* tok_seq, const int* seq_off,
+                   const int* past, long tokens, int dtype, cudaStream_t s) {
+  if (tokens == 0) return 0;
+  if (D > QK_MAXD || rot > D || (rot & 1)) return -1;
+  const size_t smem = (size_t)(rot + 32) * sizeof(float);
+  if (dtype) qk_prepare_kernel<bf16><<<(unsigned)tokens, 128, smem, s>>>((bf16*)q, ldq, (bf16*)k, ldk, (const bf16*)qw, (const bf16*)kw,
+      freq, mscale, rot, H, G, D, eps, full_norm, unit_norm, tok_seq, seq_off, past);
+  else qk_prepare_kernel<float><<<(unsigned)tokens, 128, smem, s>>>((float*)q, ldq, (float*)k, ldk, (const float*)qw, (const float*)kw,
+      freq, mscale, rot, H, G, D, eps, full_norm, unit_norm, tok_seq, seq_off, past);
+  LAUNCH_END();
+}
+
+int lbk_kv_write(void* ring, void* first, const void* knew, const void* vnew, long ldn, const int* tok_seq, const int* seq_off,
+                 const int* slots, const int* past, long tokens, int KC, int VC, int L, int nfirst, int dtype, cudaStream_t s) {
+  if (tokens == 0) return 0;
+  if (dtype) kv_write_kernel<bf16><<<(unsigned)tokens, 128, 0, s>>>((bf16*)ring, (bf16*)first, (const bf16*)knew, (const bf16*)vnew, ldn,
+      tok_seq, seq_off, slots, past, KC, VC, L, nfirst);
+  else kv_write_kernel<float><<<(unsigned)tokens, 128, 0, s>>>((float*)ring, (float*)first, (const float*)knew, (const float*)vnew, ldn,
+      tok_seq, seq_off, slots, past, KC, VC, L, nfirst);
+  LAUNCH_END();
+}
+
+int lbk_kv_gather(const void* ring, const void* first, const void* knew, const void* vnew, long ldn, const int* ext_seq,
+                  const int* ext_off, const int* nsink, const int* cstart, const int* seq_off, const int* slots, const int* past,
+                  void* ext, long rows, int KC, int VC, int L, int nfirst, int dtype, cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (dtype) kv_gather_kernel<bf16><<<(unsigned)rows, 128, 0, s>>>((const bf16*)ring, (const bf16*)first, (const bf16*)knew,
+      (const bf16*)vnew, ldn, ext_seq, ext_off, nsink, cstart, seq_off, slots, past, (bf16*)ext, KC, VC, L, nfirst);
+  else kv_gather_kernel<float><<<(unsigned)rows, 128, 0, s>>>((const float*)ring, (const float*)first, (const float*)knew,
+      (const float*)vnew, ldn, ext_seq, ext_off, nsink, cstart, seq_off, slots, past, (float*)ext, KC, VC, L, nfirst);
+  LAUNCH_END();
+}
+
+int lbk_masked_attention(const void* q, long ldq, const void* kbase, const void* vbase, long ldkv, const void* ring, const void* first,
+                         int L, int nfirst, const int* ext_off, const int* nsink, const int* cstart, const int* slots,
+                         const void* gate, long ldg, const int* tok_seq, const int* seq_off, const int* past, void* y, long ldy,
+                         long tokens, int H, int G, int D, int V, int window, int chunk, int keep, float scale, int dtype,
+                         cudaStream_t s) {
+  if (tokens == 0) return 0;
+  if (V > 32 * ATT_MAXV || G <= 0 || H % G) return -1;
+  KvSource src{kbase, vbase, ldkv, ring, first, L, nfirst, G * (D + V), G * D, ext_off, nsink, cstart, slots};
+  const int warps = 4;
+  const long nwarps = tokens * H;
+  const unsigned grid = (unsigned)((nwarps + warps - 1) / warps);
+  const size_t smem = (size_t)warps * D * sizeof(float);
+  if (dtype) masked_attention_kernel<bf16><<<grid, warps * 32, smem, s>>>((const bf16*)q, ldq, src, (const bf16*)gate, ldg, tok_seq,
+      seq_off, past, (bf16*)y, ldy, tokens, H, G, D, V, window, chunk, keep, scale);
+  else masked_attention_kernel<float><<<grid, warps * 32, smem, s>>>((const float*)q, ldq, src, (const float*)gate, ldg, tok_seq,
+      seq_off, past, (float*)y, ldy, tokens, H, G, D, V, window, chunk, keep, scale);
+  LAUNCH_END();
+}
+
+int lbk_moe_route(const void* h, long ldh, const void* wr, int E, int n, int top, float rscale, int* idx, float* wts, int* counts,
+                  long tokens, int dtype, cudaStream_t s) {
+  if (tokens == 0) return 0;
+  if (top > E) return -1;
+  int warps = 4;
+  while (warps > 1 && (size_t)warps * (n + E) * sizeof(float) > 96 * 1024) warps >>= 1;
+  const size_t smem = (size_t)warps * (n + E) * sizeof(float);
+  if (smem > 200 * 1024) return -1;
+  const unsigned grid = (unsigned)((tokens + warps - 1) / warps);
+  if (dtype) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    moe_route_kernel<bf16><<<grid, warps * 32, smem, s>>>((const bf16*)h, ldh, (const bf16*)wr, E, n, top, rscale, idx, wts, counts, tokens);
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    moe_route_kernel<float><<<grid, warps * 32, smem, s>>>((const float*)h, ldh, (const float*)wr, E, n, top, rscale, idx, wts, counts, tokens);
+  }
+  LAUNCH_END();
+}
+
+int lbk_moe_pairs(const void* h, long ldh, const void* wgu, const void* wd, const int* idx, const float* wts, void* a, float* out,
+                  long tokens, int ff, int n, int top, int act, int dtype, cudaStream_t s) {
+  if (tokens == 0) return 0;
+  const size_t smem1 = (size_t)n * sizeof(float), smem2 = (size_t)top * ff * sizeof(float);
+  if (smem1 > 200 * 1024 || smem2 > 200 * 1024) return -1;
+  const long pairs = tokens * top;
+  // enough blocks to fill the device with few pairs, never less than 8 rows per block
+  int sy1 = (int)((148 * 4 + pairs - 1) / pairs); if (sy1 > (ff + 7) / 8) sy1 = (ff + 7) / 8; if (sy1 < 1) sy1 = 1;
+  int sy2 = (int)((148 * 4 + tokens - 1) / tokens); if (sy2 > (n + 7) / 8) sy2 = (n + 7) / 8; if (sy2 < 1) sy2 = 1;
+  if (dtype) {
+    if (smem1 > 48 * 1024) cudaFuncSetAttribute(moe_pair_gateup_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+    if (smem2 > 48 * 1024) cudaFuncSetAttribute(moe_pair_down_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+    moe_pair_gateup_kernel<bf16><<<dim3((unsigned)pairs, sy1), 256, smem1, s>>>((const bf16*)h, ldh, (const bf16*)wgu, idx, (bf16*)a, ff, n, top, act);
+    moe_pair_down_kernel<bf16><<<dim3((unsigned)tokens, sy2), 256, smem2, s>>>((const bf16*)a, (const bf16*)wd, idx, wts, out, ff, n, top);
+  } else {
+    if (smem1 > 48 * 1024) cudaFuncSetAttribute(moe_pair_gateup_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+    if (smem2 > 48 * 1024) cudaFuncSetAttribute(moe_pair_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+    moe_pair_gateup_kernel<float><<<dim3((unsigned)pairs, sy1), 256, smem1, s>>>((const float*)h, ldh, (const float*)wgu, idx, (float*)a, ff, n, top, act);
+    moe_pair_down_kernel<float><<<dim3((unsigned)tokens, sy2), 256, smem2, s>>>((const float*)a, (const float*)wd, idx, wts, out, ff, n, top);
+  }
+  LAUNCH_END();
+}
+
+int lbk_moe_sort(const void* h, long ldh, const int* idx, const int* counts, int* offsets, int* cursor, int* pos, void* xs, long tokens,
+                 int E, int n, int top, int dtype, cudaStream_t s) {
+  if (tokens == 0) return 0;
+  moe_offsets_kernel<<<1, 32, 0, s>>>(counts, offsets, cursor, E);
+  const unsigned pairs = (unsigned)(tokens * top);
+  if (dtype) moe_scatter_kernel<bf16><<<pairs, 128, 0, s>>>((const bf16*)h, ldh, idx, offsets, cursor, pos, (bf16*)xs, n, top);
+  else moe_scatter_kernel<float><<<pairs, 128, 0, s>>>((const float*)h, ldh, idx, offsets, cursor, pos, (float*)xs, n, top);
+  LAUNCH_END();
+}
+
+int lbk_masked_attention_mma(const void* q, long ldq, const void* kbase, const void* vbase, long ldkv, const int* ext_off,
+                             const int* nsink, const int* cstart, const void* gate, long ldg, const int* qt_seq, const int* qt_start,
+                             int n_qtiles, const int* seq_off, const int* past, void* y, long ldy, int H, int G, int D, int V,
+                             int window, int chunk, int keep, float scale, cudaStream_t s) {
+  return -1;
+}
+
+int lbk_ring_decode(const void* q, long ldq, const void* ring, const void* first, int L, int nfirst, const int* slots, const int* past,
+                    const void* gate, long ldg, void* y, long ldy, float* part, int B, int H, int G, int D, int V, int window,
+                    int chunk, int keep, float scale, int splits, int dtype, cudaStream_t s) {
+  return -1;
+}
+
+}  // extern "C"

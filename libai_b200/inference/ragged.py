@@ -28,6 +28,40 @@ class WindowExt:
         self.ext_off, self.ext_seq = packed[: rb.B + 1], packed[rb.B + 1:]
 
 
+def mask_floor(position: int, window: int, chunk: int) -> int:
+    """First position of the contiguous range that the query at ``position`` sees under a chunk mask (``chunk > 0``: its own
+    chunk, counted from position 0) or a sliding window (``window > 0``); 0 when neither bounds it."""
+    if chunk > 0:
+        return (position // chunk) * chunk
+    if window > 0:
+        return max(0, position - window + 1)
+    return 0
+
+
+class KvExt:
+    """Row layout of the keys / values of a prompt step over ring caches, shared by every layer that reads the same cache
+    (each with its own mask ``(window, chunk, keep)``): per sequence the kept-first positions that are older than the
+    contiguous part (``nsink`` rows, positions 0 …), the cached positions ``cstart … past − 1``, then the step's own rows.
+    ``cstart`` is the earliest position the step's first query sees under any of the masks."""
+
+    def __init__(self, rb: "RaggedBatch", masks):
+        self.cstart_list = [min(mask_floor(p, w, c) for w, c, _ in masks) for p in rb.past_list]
+        keep = max([k for w, c, k in masks if c <= 0] + [0])
+        self.nsink_list = [min(keep, cs) for cs in self.cstart_list]
+        lens = [ns + (p - cs) + n for ns, cs, p, n in zip(self.nsink_list, self.cstart_list, rb.past_list, rb.lens)]
+        self.offsets = [0]
+        for n in lens:
+            self.offsets.append(self.offsets[-1] + n)
+        self.rows = self.offsets[-1]
+        self.cached = any(ns + p - cs > 0 for ns, cs, p in zip(self.nsink_list, self.cstart_list, rb.past_list))
+        seq = [b for b, n in enumerate(lens) for _ in range(n)] if self.cached else []
+        packed = torch.tensor(self.offsets + self.nsink_list + self.cstart_list + seq, dtype=torch.int32)
+        packed = packed.to(rb.device, non_blocking=True)
+        B = rb.B
+        self.ext_off, self.nsink, self.cstart = packed[: B + 1], packed[B + 1: 2 * B + 1], packed[2 * B + 1: 3 * B + 1]
+        self.ext_seq = packed[3 * B + 1:]
+
+
 class RaggedBatch:
     def __init__(self, lens: Sequence[int], slots: Sequence[int], past: Sequence[int], device):
         assert len(lens) == len(slots) == len(past) and all(n > 0 for n in lens)
@@ -45,12 +79,20 @@ class RaggedBatch:
         self.seq_off, self.slots, self.past = packed[: B + 1], packed[B + 1: 2 * B + 1], packed[2 * B + 1: 3 * B + 1]
         self.tok_seq = packed[3 * B + 1:]
         self._ext: Dict[int, WindowExt] = {}
+        self._kv_ext: Dict[tuple, KvExt] = {}
         self._tiles: Dict[int, tuple] = {}
 
     def ext(self, window: int) -> WindowExt:
         if window not in self._ext:
             self._ext[window] = WindowExt(self, window)
         return self._ext[window]
+
+    def kv_ext(self, masks) -> KvExt:
+        """Key / value row layout of this step for a cache read under the masks ``((window, chunk, keep), …)``."""
+        key = tuple(sorted(set(tuple(m) for m in masks)))
+        if key not in self._kv_ext:
+            self._kv_ext[key] = KvExt(self, key)
+        return self._kv_ext[key]
 
     def query_tiles(self, size: int):
         """Tiles of ``size`` consecutive new tokens of one sequence: (sequence of every tile, its first token) on the device."""

@@ -17,3 +17,6 @@ __all__ = [
 ]
 from .delta_rule import GatedDeltaMixer
 from .latent_attention import LatentAttention
+from .layer_norm import DynamicTanh
+from .moe import MoEFeedForward
+from .ring_attention import RingAttention

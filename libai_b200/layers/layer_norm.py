@@ -6,6 +6,7 @@ Under sequence parallelism the parameters see only ``1/t`` of the tokens per ran
 gradients are summed over the TP group (flag ``sequence_parallel`` on the parameter, consumed by
 the gradient-sync engine).
 """
+import torch
 from torch import nn
 
 from libai_b200.ops import functional as OF
@@ -85,3 +86,35 @@ class RMSLayerNorm(nn.Module):
 
     def extra_repr(self) -> str:
         return f"{self.normalized_shape}, eps={self.eps}"
+
+
+class DynamicTanh(nn.Module):
+    """Dynamic Tanh in the place of a norm: ``tanh(alpha · x) · weight + bias`` with a learned scalar ``alpha``; no mean or
+    variance is computed (Zhu et al., "Transformers without Normalization", 2025)."""
+
+    def __init__(self, normalized_shape, alpha_init=0.5, *, layer_idx=0, dtype=None):
+        super().__init__()
+        if isinstance(normalized_shape, int):
+            normalized_shape = (normalized_shape,)
+        self.normalized_shape = tuple(normalized_shape)
+        self.layer_idx = layer_idx
+        self.weight = create_parameter(self.normalized_shape, ones_, layer_idx=layer_idx, dtype=dtype)
+        self.bias = create_parameter(self.normalized_shape, zeros_, layer_idx=layer_idx, dtype=dtype)
+        self.alpha = create_parameter((), lambda t: t.fill_(alpha_init), layer_idx=layer_idx, dtype=dtype)
+
+    def forward(self, x):
+        return (torch.tanh(self.alpha.float() * x.float()) * self.weight.float() + self.bias.float()).to(x.dtype)
+
+    def triple(self):
+        """``(weight, bias, alpha)`` as the fused residual operator takes them."""
+        return self.weight, self.bias, self.alpha
+
+    def rows(self, x, out):
+        """Inference form on 2-D row views: ``x`` is the fp32 residual stream, ``out`` has the compute dtype."""
+        from libai_b200.ops import kv_functional as KF
+
+        KF.dyt_residual(x, nxt=self.triple(), h=out)
+        return out
+
+    def extra_repr(self) -> str:
+        return f"{self.normalized_shape}"

@@ -1,6 +1,7 @@
 from .bert_model import BertForClassification, BertForPreTraining, BertModel
 from .build import build_graph, build_model
 from .bumodra_model import BumodraForCausalLM, BumodraModel
+from .nefelorn_model import NefelornForCausalLM, NefelornModel
 from .gpt_model import GPTForPreTraining, GPTModel
 from .llama_model import LlamaForCausalLM, LlamaModel
 from .resmlp import ResMLP
@@ -18,5 +19,5 @@ __all__ = [
     "T5Model", "T5ForPreTraining",
     "VisionTransformer", "SwinTransformer", "SwinTransformerV2", "ResMLP",
     "LlamaModel", "LlamaForCausalLM",
-    "BumodraModel", "BumodraForCausalLM",
+    "BumodraModel", "BumodraForCausalLM", "NefelornModel", "NefelornForCausalLM",
 ]

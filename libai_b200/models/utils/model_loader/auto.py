@@ -28,10 +28,28 @@ def _bumodra():
     return BumodraForCausalLM, BumodraLoader, {}
 
 
+def _nefelorn():
+    from libai_b200.models import NefelornForCausalLM
+    from .nefelorn_loader import NefelornLoader
+
+    return NefelornForCausalLM, NefelornLoader, {}
+
+
 ARCHITECTURES = {
     "bumodra": _bumodra,
+    "nefelorn": _nefelorn,
     "llama": _llama, "llamaforcausallm": _llama,
 }
+
+
+# native libraries (``libai_b200.ops.build``) that a model's generation path launches besides the GEMM library ``_C``
+NATIVE_LIBS = {"bumodra": ["_C_seq"], "nefelorn": ["_C_kv"]}
+
+
+def native_libs_of(path: str, dtype=torch.bfloat16):
+    """Names of the in-tree libraries that serving the checkpoint at ``path`` in ``dtype`` needs: the model's own kernels, and
+    the tcgen05 GEMM library only where bf16 products run on it."""
+    return NATIVE_LIBS.get(architecture_of(path), []) + (["_C"] if dtype == torch.bfloat16 else [])
 
 
 def architecture_of(path: str) -> str:

@@ -97,6 +97,27 @@ def load_seq_ext():
     return _SEQ_EXT
 
 
+_KV_EXT = None
+_KV_SO_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_C_kv.so")
+
+
+def load_kv_ext():
+    """Load ``libai_b200/_C_kv.so`` (ring key/value caches, masked attention, Dynamic-Tanh norms, mixture of experts) once; it
+    is compiled in-tree on first use when the checkout has no built copy yet.  Returns ``torch.ops.libai_b200_kv``."""
+    global _KV_EXT
+    if _KV_EXT is not None:
+        return _KV_EXT
+    with _LOCK:
+        if _KV_EXT is None:
+            if not os.path.exists(_KV_SO_PATH):
+                from . import build as _build
+
+                _build.build(only=["_C_kv"])
+            torch.ops.load_library(_KV_SO_PATH)
+            _KV_EXT = _FastOps(torch.ops.libai_b200_kv)
+    return _KV_EXT
+
+
 def use_native(*tensors) -> bool:
     """True when the native sm_100a kernel must be used for these tensors."""
     if impl() != "native":

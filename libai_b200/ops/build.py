@@ -1,7 +1,8 @@
 """In-tree build of the native extensions: ``libai_b200/_C.so`` (GEMM, attention, norms, optimizer, collectives) and
-``libai_b200/_C_seq.so`` (ragged-batch sequence mixers with per-sequence state).
+``libai_b200/_C_seq.so`` (ragged-batch sequence mixers with per-sequence state) and ``libai_b200/_C_kv.so`` (ring key/value
+caches, masked grouped-query attention, Dynamic-Tanh norms, mixture of experts).
 
-    python -m libai_b200.ops.build [--force] [--verbose] [--only _C|_C_seq]
+    python -m libai_b200.ops.build [--force] [--verbose] [--only _C|_C_seq|_C_kv]
 
 CUDA sources are compiled for sm_100a only (``-gencode arch=compute_100a,code=sm_100a -lineinfo``);
 nvcc cross-compiles without a GPU.  Objects are cached under ``libai_b200/csrc/build`` keyed by
@@ -28,6 +29,9 @@ CPP_SOURCES = ["bindings.cpp", "symm_mem.cpp"]
 SEQ_SO_PATH = os.path.join(ROOT, "_C_seq.so")
 SEQ_CU_SOURCES = ["seq_mixers.cu"]
 SEQ_CPP_SOURCES = ["seq_bindings.cpp"]
+KV_SO_PATH = os.path.join(ROOT, "_C_kv.so")
+KV_CU_SOURCES = ["kv_mixers.cu"]
+KV_CPP_SOURCES = ["kv_bindings.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "--use_fast_math", "-std=c++17",
@@ -54,7 +58,9 @@ def _stale(src, obj, deps=()):
 
 
 def build(force: bool = False, verbose: bool = False, only=None) -> str:
-    """Build the libraries named in ``only`` (default: both); returns the path of ``_C.so``."""
+    """Build the libraries named in ``only`` (default: all); returns the path of ``_C.so``."""
+    if only is None or "_C_kv" in only:
+        _build_lib(KV_SO_PATH, KV_CU_SOURCES, KV_CPP_SOURCES, SEQ_NVCC_FLAGS, "_C_kv", force, verbose)
     if only is None or "_C_seq" in only:
         _build_lib(SEQ_SO_PATH, SEQ_CU_SOURCES, SEQ_CPP_SOURCES, SEQ_NVCC_FLAGS, "_C_seq", force, verbose)
     if only is None or "_C" in only:
@@ -109,6 +115,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
-    ap.add_argument("--only", action="append", choices=["_C", "_C_seq"])
+    ap.add_argument("--only", action="append", choices=["_C", "_C_seq", "_C_kv"])
     a = ap.parse_args()
     print(build(a.force, a.verbose, a.only))

@@ -1,0 +1,370 @@
+"""Operators of decoders that keep keys and values in per-sequence rings (``csrc/kv_mixers.cu``): Dynamic-Tanh norms fused
+around the fp32 residual sum, query/key preparation (RMS norms, rotary positions with per-dimension frequencies), the ring /
+kept-first-token cache, grouped-query attention under a position mask and a mixture-of-experts feed-forward.
+
+Every operator takes the step's :class:`~libai_b200.inference.ragged.RaggedBatch`.  On a CUDA device the native kernels run
+(a missing extension is an error, there is no fallback); on the CPU the same operators are plain PyTorch, sequence by
+sequence, which is what the CPU tests use.  Norms, softmax, the router and the residual sum are fp32 in both.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import count_launch, impl, load_kv_ext
+from .seq_functional import _tcgen05_gemm, linear, linear_accumulate  # noqa: F401  (projections are shared)
+
+ACT_COPY, ACT_GELU, ACT_SILU, ACT_GELU_TANH, ACT_RELU2 = 0, 1, 2, 3, 4
+ACTS = {"copy": ACT_COPY, "gelu": ACT_GELU, "silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "relu2": ACT_RELU2}
+
+
+def _native(t: torch.Tensor) -> bool:
+    return t.is_cuda and impl() == "native"
+
+
+def _act(v, act: int):
+    if act == ACT_GELU:
+        return F.gelu(v)
+    if act == ACT_SILU:
+        return F.silu(v)
+    if act == ACT_GELU_TANH:
+        return F.gelu(v, approximate="tanh")
+    if act == ACT_RELU2:
+        return torch.relu(v) ** 2
+    return v
+
+
+# ------------------------------------------------------------------------------------------------------------ projections
+def linear_into(a, w, out):
+    """``out = a @ wᵀ`` into a given row-major matrix (bf16, or fp32 so that a sublayer's output reaches its norm unrounded):
+    the tcgen05 GEMM writes it from its epilogue; shapes it does not take, fp32 operands and CPU tensors go to the vendor /
+    PyTorch product."""
+    from . import use_native
+
+    if (a.is_cuda and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and use_native(a) and a.dim() == 2
+            and a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.shape[1] % 8 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0
+            and w.shape[0] % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+            and out.stride(0) % 8 == 0 and a.shape[0] > 0):
+        if _tcgen05_gemm(a, w, out, False, out.dtype) is not None:
+            return out
+    if out.dtype == a.dtype:
+        return torch.mm(a, w.t(), out=out) if out.is_contiguous() else out.copy_(F.linear(a, w))
+    return out.copy_(F.linear(a, w))
+
+
+def linear_f32(a, w):
+    """``a @ wᵀ`` as a fresh fp32 matrix."""
+    return linear_into(a, w, torch.empty(a.shape[0], w.shape[0], dtype=torch.float32, device=a.device))
+
+
+# ------------------------------------------------------------------------------------------------------- stream and norms
+def embed_scale(table, ids, scale: float, x):
+    """``x[r] = table[ids[r]] · scale`` into the fp32 stream ``x``."""
+    if _native(table):
+        count_launch()
+        load_kv_ext().embed_scale(table, ids, float(scale), x)
+        return x
+    x.copy_(table[ids].float() * scale)
+    return x
+
+
+def dyt_residual(x, y=None, post=None, nxt=None, h=None, pos=None, cw=None):
+    """The residual update around a sublayer with Dynamic-Tanh norms, ``dyt(v; w, b, α) = tanh(α v)·w + b``:
+    ``x += dyt(y; post)`` when ``y`` is given, then ``h = dyt(x; nxt)`` when ``h`` is given.  ``x`` is the fp32 stream
+    (updated in place); ``post`` / ``nxt`` are ``(w, b, alpha)``.  With ``pos`` / ``cw`` ``[rows, top]`` the sublayer output
+    of row r is gathered, ``Σ_k cw[r, k] · y[pos[r, k]]`` (expert outputs sorted by expert)."""
+    if _native(x):
+        count_launch()
+        pw, pb, pa = post if y is not None else (None, None, None)
+        nw, nb, na = nxt if h is not None else (None, None, None)
+        load_kv_ext().dyt_residual(x, y, pos, cw, pw, pb, pa, nw, nb, na, h)
+        return x
+    if y is not None:
+        yv = y.float()
+        if pos is not None:
+            yv = (yv[pos.long()] * cw[:, :, None]).sum(1)
+        w, b, a = post
+        x.add_(torch.tanh(a.float() * yv) * w.float() + b.float())
+    if h is not None:
+        w, b, a = nxt
+        h.copy_(torch.tanh(a.float() * x) * w.float() + b.float())
+    return x
+
+
+def act_rows(inp, out, act: int, gated: bool = False):
+    """``out = act(inp)``, or — ``gated`` — ``out = act(inp[:, :n]) · inp[:, n:]`` (column slices of row-major matrices)."""
+    if _native(inp):
+        count_launch()
+        load_kv_ext().act_rows(inp, out, act, gated)
+        return out
+    n = out.shape[1]
+    v = _act(inp[:, :n].float(), act)
+    if gated:
+        v = v * inp[:, n:].float()
+    out.copy_(v)
+    return out
+
+
+def softcap(logits, cap: float):
+    """``logits ← cap · tanh(logits / cap)`` in place (fp32)."""
+    if _native(logits):
+        count_launch()
+        load_kv_ext().softcap(logits, float(cap))
+        return logits
+    return logits.copy_(cap * torch.tanh(logits / cap))
+
+
+# ------------------------------------------------------------------------------------------------------- rotary positions
+def rotary_frequencies(dims: int, base: float, scaling: Optional[dict] = None):
+    """Per-pair angular frequencies ``[dims/2]`` (fp32) and the factor on cos / sin.  Plain: ``f_i = base^(-2i/dims)``, factor 1.
+    With ``scaling`` = ``{factor, original, fast, slow}`` the frequencies are blended per dimension between ``f_i`` (dimensions
+    that turn more than ``fast`` times within ``original`` positions) and ``f_i / factor`` (fewer than ``slow`` turns), linearly
+    in the dimension index in between, and cos / sin are multiplied by ``0.1 ln(factor) + 1``."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = float(base) ** (-2.0 * i / dims)
+    mscale = 1.0
+    if scaling:
+        factor, original = float(scaling["factor"]), float(scaling["original"])
+
+        def turns_dim(t):
+            return dims * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(base))
+
+        lo = max(math.floor(turns_dim(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(turns_dim(float(scaling["slow"]))), dims - 1)
+        ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        f = f / factor * ramp + f * (1.0 - ramp)
+        mscale = 0.1 * math.log(factor) + 1.0
+    return f.float(), mscale
+
+
+def qk_prepare(q, k, qw, kw, freq, mscale: float, rb, H: int, G: int, D: int, eps: float, full_norm: bool, unit_norm: bool):
+    """Query / key preparation in place on the packed rows ``q`` ``[tokens, H·D]`` and ``k`` ``[tokens, G·D]`` (or ``None``):
+    ``full_norm`` — RMS norm over the whole projection with weights ``qw`` / ``kw`` (before rotation); rotation of the first
+    ``2·len(freq)`` channels of every head (channel i with i + len(freq)) by ``position · freq[i]``; ``unit_norm`` — every head
+    divided by its root mean square (after rotation)."""
+    if _native(q):
+        count_launch()
+        load_kv_ext().qk_prepare(q, k, qw if full_norm else None, kw if (full_norm and k is not None) else None, freq, float(mscale),
+                                 H, G, D, float(eps), full_norm, unit_norm, rb.tok_seq, rb.seq_off, rb.past)
+        return
+    half = freq.numel()
+    pos = torch.cat([torch.arange(p, p + n) for p, n in zip(rb.past_list, rb.lens)]).to(q.device).float()
+    ang = pos[:, None] * freq.float()[None, :]
+    cos, sin = (ang.cos() * mscale)[:, None, :], (ang.sin() * mscale)[:, None, :]
+    for t, w, heads in ((q, qw, H), (k, kw, G)):
+        if t is None:
+            continue
+        v = t.float()
+        if full_norm:
+            v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+        v = v.view(-1, heads, D)
+        a, b = v[..., :half], v[..., half:2 * half]
+        v = torch.cat([a * cos - b * sin, b * cos + a * sin, v[..., 2 * half:]], -1)
+        if unit_norm:
+            v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+        t.copy_(v.reshape(-1, heads * D))
+
+
+# ----------------------------------------------------------------------------------------------------------- cache rows
+def kv_write(ring, first, knew, vnew, rb):
+    """Store the step's key / value rows: position p of a sequence goes to ``ring[slot, p % L]`` and, for ``p < nfirst``, to
+    ``first[slot, p]``."""
+    if _native(knew):
+        count_launch()
+        load_kv_ext().kv_write(ring, first, knew, vnew, rb.tok_seq, rb.seq_off, rb.slots, rb.past)
+        return
+    L, nf = ring.shape[1], first.shape[1]
+    for b in range(rb.B):
+        lo, n, slot, past = rb.offsets[b], rb.lens[b], rb.slot_list[b], rb.past_list[b]
+        for t in range(n):
+            row = torch.cat([knew[lo + t], vnew[lo + t]])
+            if n - t <= L:
+                ring[slot, (past + t) % L] = row
+            if past + t < nf:
+                first[slot, past + t] = row
+    return
+
+
+def kv_gather(ring, first, knew, vnew, rb, ext):
+    """The key / value rows a prompt step reads (``ext``: a :class:`~libai_b200.inference.ragged.KvExt`): per sequence the
+    kept-first rows older than the contiguous part, the cached contiguous part, the step's own rows."""
+    out = torch.empty(ext.rows, ring.shape[2], dtype=ring.dtype, device=ring.device)
+    if _native(knew):
+        count_launch()
+        load_kv_ext().kv_gather(ring, first, knew, vnew, ext.ext_seq, ext.ext_off, ext.nsink, ext.cstart, rb.seq_off, rb.slots, rb.past, out)
+        return out
+    L = ring.shape[1]
+    for b in range(rb.B):
+        lo, n, slot, past = rb.offsets[b], rb.lens[b], rb.slot_list[b], rb.past_list[b]
+        at = ext.offsets[b]
+        for p in range(ext.nsink_list[b]):
+            out[at] = first[slot, p]
+            at += 1
+        for p in range(ext.cstart_list[b], past):
+            out[at] = ring[slot, p % L]
+            at += 1
+        out[at:at + n] = torch.cat([knew[lo:lo + n], vnew[lo:lo + n]], 1)
+    return out
+
+
+def _visible(pi: int, window: int, chunk: int, keep: int):
+    """Positions the query at ``pi`` sees, in ascending order."""
+    if chunk > 0:
+        lo = (pi // chunk) * chunk
+    elif window > 0:
+        lo = max(0, pi - window + 1)
+    else:
+        lo = 0
+    first = list(range(min(keep, lo))) if chunk <= 0 else []
+    return first + list(range(lo, pi + 1))
+
+
+def _attend_rows(qrow, keys, vals, H, G, D, V, scale):
+    """``qrow`` ``[H·D]``; ``keys`` ``[n, G·D]``, ``vals`` ``[n, G·V]`` → ``[H, V]`` fp32."""
+    rep = H // G
+    k = keys.float().view(-1, G, D).repeat_interleave(rep, 1)
+    v = vals.float().view(-1, G, V).repeat_interleave(rep, 1)
+    s = torch.einsum("hd,jhd->hj", qrow.float().view(H, D), k) * scale
+    return torch.einsum("hj,jhv->hv", torch.softmax(s, -1), v)
+
+
+def masked_attention(q, kmat, vmat, ext, gate, rb, y, H: int, G: int, D: int, V: int, window: int, chunk: int, keep: int,
+                     scale: float, mma: bool = True):
+    """Grouped-query softmax attention of every packed query over the rows of the ext matrix (``kmat`` ``[rows, G·D]``,
+    ``vmat`` ``[rows, G·V]``: column slices with one row stride) that its mask admits: position j ≤ i with
+    ``j ≥ ⌊i/chunk⌋·chunk`` (``chunk > 0``) or ``j > i − window or j < keep`` (``window > 0``).  Head h of the result is
+    multiplied by ``sigmoid(gate[t, h])`` when a gate is given.  bf16 inputs with head sizes the tensor-core kernel is built for
+    take it; ``mma=False`` keeps them on the generic kernel (fp32 inputs always are)."""
+    if _native(q):
+        count_launch()
+        tiles = (None, None)
+        if mma and q.dtype == torch.bfloat16 and mma_eligible(q, kmat, vmat, y, D, V):
+            tiles = rb.query_tiles(64)
+        load_kv_ext().masked_attention(q, kmat, vmat, ext.ext_off, ext.nsink, ext.cstart, gate, rb.tok_seq, rb.seq_off, rb.past,
+                                       tiles[0], tiles[1], y, H, G, D, V, window, chunk, keep, float(scale))
+        return y
+    for b in range(rb.B):
+        lo, n, past, eo, ns, cs = rb.offsets[b], rb.lens[b], rb.past_list[b], ext.offsets[b], ext.nsink_list[b], ext.cstart_list[b]
+        for t in range(n):
+            rows = [eo + (p if p < cs else ns + p - cs) for p in _visible(past + t, window, chunk, keep)]
+            o = _attend_rows(q[lo + t], kmat[rows], vmat[rows], H, G, D, V, scale)
+            if gate is not None:
+                o = o * torch.sigmoid(gate[lo + t].float())[:, None]
+            y[lo + t] = o.reshape(-1).to(y.dtype)
+    return y
+
+
+MMA_HEAD_SIZES = (32, 48, 64, 96, 128)
+
+
+def mma_eligible(q, kmat, vmat, y, D: int, V: int) -> bool:
+    return (D == V and D in MMA_HEAD_SIZES and all(t.data_ptr() % 16 == 0 and t.stride(0) % 8 == 0 for t in (q, kmat, vmat, y)))
+
+
+def ring_attention(q, ring, first, gate, rb, y, H: int, G: int, D: int, V: int, window: int, chunk: int, keep: int, scale: float,
+                   splits: Optional[int] = None):
+    """Single-token steps: the same attention with keys and values read straight from ``ring`` / ``first`` (the step's own row
+    has been written).  ``splits``: 0 = one warp per (token, head); n > 0 = the grouped kernel with the visible keys of a
+    (sequence, key head) cut into n parts; ``None`` chooses by the mask's reach."""
+    if _native(q):
+        if splits is None:
+            reach = (chunk if chunk > 0 else window) + keep
+            splits = 0 if (reach <= 64 or H // G > 8 or V > 128 or D > 256) else max(1, min(32, (reach + 127) // 128))
+        count_launch(1 if splits == 0 else 2)
+        load_kv_ext().ring_attention(q, ring, first, gate, rb.tok_seq, rb.seq_off, rb.slots, rb.past, y, H, G, D, V, window, chunk, keep,
+                                     float(scale), splits)
+        return y
+    L, nf, KC = ring.shape[1], first.shape[1], G * D
+    for b in range(rb.B):
+        slot, pi = rb.slot_list[b], rb.past_list[b]
+        rows = torch.stack([first[slot, p] if p < nf else ring[slot, p % L] for p in _visible(pi, window, chunk, keep)])
+        o = _attend_rows(q[b], rows[:, :KC], rows[:, KC:], H, G, D, V, scale)
+        if gate is not None:
+            o = o * torch.sigmoid(gate[b].float())[:, None]
+        y[b] = o.reshape(-1).to(y.dtype)
+    return y
+
+
+# ------------------------------------------------------------------------------------------------------ mixture of experts
+def moe_route(h, wr, top: int, rscale: float, counts=None):
+    """Router: ``s = sigmoid(W_r h)`` in fp32, the ``top`` largest scores, weights ``s / (Σ s + 1e-20) · rscale``.  Returns
+    ``idx`` int32 and ``wts`` fp32, both ``[tokens, top]``; ``counts`` (int32 ``[E]``, zeroed by the caller) receives the number
+    of tokens of every expert."""
+    T = h.shape[0]
+    idx = torch.empty(T, top, dtype=torch.int32, device=h.device)
+    wts = torch.empty(T, top, dtype=torch.float32, device=h.device)
+    if _native(h):
+        count_launch()
+        load_kv_ext().moe_route(h, wr, top, float(rscale), idx, wts, counts)
+        return idx, wts
+    s = torch.sigmoid(F.linear(h.float(), wr.float()))
+    tv, ti = s.topk(top, -1)
+    idx.copy_(ti)
+    wts.copy_(tv / (tv.sum(-1, keepdim=True) + 1e-20) * rscale)
+    if counts is not None:
+        counts.add_(torch.bincount(ti.reshape(-1), minlength=counts.numel()).to(counts.dtype))
+    return idx, wts
+
+
+def moe_pairs(h, wgu, wd, idx, wts, act: int):
+    """Experts for few tokens: every (token, chosen expert) pair reads its expert's matrices.  ``wgu`` ``[E, 2·ff, width]``
+    (gate rows, then up rows), ``wd`` ``[E, width, ff]``.  Returns ``Σ_k wts[t,k] · W_down,k (act(W_gate,k h) · W_up,k h)`` as
+    fp32 ``[tokens, width]``."""
+    T, n = h.shape
+    top, ff = idx.shape[1], wgu.shape[1] // 2
+    out = torch.empty(T, n, dtype=torch.float32, device=h.device)
+    if _native(h):
+        count_launch(2)
+        a = torch.empty(T * top, ff, dtype=h.dtype, device=h.device)
+        load_kv_ext().moe_pairs(h, wgu, wd, idx, wts, a, out, act)
+        return out
+    for t in range(T):
+        acc = torch.zeros(n)
+        for k in range(top):
+            e = int(idx[t, k])
+            gu = wgu[e].float() @ h[t].float()
+            a = (_act(gu[:ff], act) * gu[ff:]).to(h.dtype).float()
+            acc += wts[t, k] * (wd[e].float() @ a)
+        out[t] = acc
+    return out
+
+
+def moe_sorted(h, wgu, wd, idx, counts, act: int):
+    """Experts for many tokens: the rows are copied into a matrix sorted by expert, every expert runs as two dense products on
+    its row range (the framework's GEMM), and the caller gathers the weighted sum (:func:`dyt_residual` with ``pos``).  Returns
+    ``(ys fp32 [tokens·top, width], pos int32 [tokens, top])``: the output row of pair (t, k) is ``ys[pos[t, k]]``.  The per-expert
+    row counts are read back by the host (one synchronisation), so this form is for prompt steps, not for captured graphs."""
+    T, n = h.shape
+    top, E, ff = idx.shape[1], wgu.shape[0], wgu.shape[1] // 2
+    P = T * top
+    dev = h.device
+    xs = torch.empty(P, n, dtype=h.dtype, device=dev)
+    pos = torch.empty(T, top, dtype=torch.int32, device=dev)
+    if _native(h):
+        count_launch(2)
+        meta = torch.empty(2 * E + 1, dtype=torch.int32, device=dev)
+        load_kv_ext().moe_sort(h, idx, counts, meta[: E + 1], meta[E + 1:], pos, xs)
+        cnt = counts.tolist()
+    else:
+        order = torch.sort(idx.reshape(-1).long(), stable=True).indices
+        pos.view(-1)[order] = torch.arange(P, dtype=torch.int32)
+        xs.copy_(h[order // top])
+        cnt = torch.bincount(idx.reshape(-1).long(), minlength=E).tolist()
+    gu = torch.empty(P, 2 * ff, dtype=h.dtype, device=dev)
+    at = 0
+    for e, c in enumerate(cnt):
+        if c:
+            linear_into(xs[at:at + c], wgu[e], gu[at:at + c])
+            at += c
+    a = torch.empty(P, ff, dtype=h.dtype, device=dev)
+    act_rows(gu, a, act, gated=True)
+    ys = torch.empty(P, n, dtype=torch.float32, device=dev)
+    at = 0
+    for e, c in enumerate(cnt):
+        if c:
+            linear_into(a[at:at + c], wd[e], ys[at:at + c])
+            at += c
+    return ys, pos
