@@ -375,6 +375,322 @@ __global__ void masked_attention_kernel(const T* __restrict__ q, long ldq, KvSou
 }
 
 // ------------------------------------------------------------------------------------------------------------------
+// The same attention for prompts on the tensor cores (bf16 operands, fp32 accumulation and softmax): a block of 4 warps
+// owns 64 consecutive queries of one (sequence, head) — 16 per warp, held as A fragments — and walks the ext rows its
+// queries can see in tiles of 64 staged through shared memory: first the kept-first rows that lie before the tile's
+// contiguous range, then the contiguous range.  S = Q Kᵀ with mma.m16n8k16, online softmax on the accumulator
+// fragments, P re-packed as A fragments, O += P V with the V fragments fetched by ldmatrix.trans.  Query tiles are
+// listed by the host (qt_seq / qt_start), so ragged batches cost no empty blocks.
+// ------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ int mask_floor(int p, int window, int chunk) {
+  return chunk > 0 ? (p / chunk) * chunk : (window > 0 ? max(0, p - window + 1) : 0);
+}
+
+template <int D, int V>
+__global__ void __launch_bounds__(128)
+masked_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long ldq, const __nv_bfloat16* __restrict__ kbase,
+                            const __nv_bfloat16* __restrict__ vbase, long ldkv, const int* __restrict__ ext_off,
+                            const int* __restrict__ nsink, const int* __restrict__ cstart, const __nv_bfloat16* __restrict__ gate, long ldg,
+                            const int* __restrict__ qt_seq, const int* __restrict__ qt_start, const int* __restrict__ seq_off,
+                            const int* __restrict__ past, __nv_bfloat16* __restrict__ y, long ldy, int H, int G, int window, int chunk,
+                            int keep, float scale) {
+  constexpr int KT = 64, KS = D + 8, VS = V + 8;
+  __shared__ __align__(16) __nv_bfloat16 Ks[KT * KS];
+  __shared__ __align__(16) __nv_bfloat16 Vs[KT * VS];
+  const int h = blockIdx.y, g = h / (H / G), b = qt_seq[blockIdx.x], t0 = qt_start[blockIdx.x];
+  const int n = seq_off[b + 1] - seq_off[b], p0 = past[b];
+  const long elo = ext_off[b];
+  const int erows = ext_off[b + 1] - ext_off[b], ns = nsink[b], cs = cstart[b];
+  const long tokbase = seq_off[b];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+  const int r0 = t0 + warp * 16 + gid, r1 = r0 + 8;                    // this lane's two query rows
+  const int pi0 = p0 + r0, pi1 = p0 + r1;                               // their positions
+  const int lo0 = mask_floor(pi0, window, chunk), lo1 = mask_floor(pi1, window, chunk);
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const int col = h * D + kk * 16 + tig * 2;
+    qf[kk][0] = r0 < n ? *reinterpret_cast<const uint32_t*>(q + (tokbase + r0) * ldq + col) : 0u;
+    qf[kk][1] = r1 < n ? *reinterpret_cast<const uint32_t*>(q + (tokbase + r1) * ldq + col) : 0u;
+    qf[kk][2] = r0 < n ? *reinterpret_cast<const uint32_t*>(q + (tokbase + r0) * ldq + col + 8) : 0u;
+    qf[kk][3] = r1 < n ? *reinterpret_cast<const uint32_t*>(q + (tokbase + r1) * ldq + col + 8) : 0u;
+  }
+  float o[V / 8][4];
+#pragma unroll
+  for (int j = 0; j < V / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;              // l: this lane's share of the row sums
+  const int p_first = p0 + t0, p_last = p0 + min(t0 + 63, n - 1);
+  const int lo_first = mask_floor(p_first, window, chunk);
+  const int nA = chunk > 0 ? 0 : min(keep, lo_first);                   // kept-first rows before the contiguous range
+  const int mrow0 = ns + lo_first - cs, mrow1 = ns + p_last - cs;       // contiguous range, as rows of this sequence
+  const int pw0 = p0 + t0 + warp * 16, pw1 = pw0 + 15;                  // positions of this warp's queries
+  const int low0 = mask_floor(pw0, window, chunk);
+  const int tilesA = (nA + KT - 1) / KT, tilesB = (mrow1 - mrow0) / KT + 1;
+  for (int it = 0; it < tilesA + tilesB; ++it) {
+    const bool phaseA = it < tilesA;
+    const int k0 = phaseA ? it * KT : mrow0 + (it - tilesA) * KT;       // first row of the tile
+    const int rlim = phaseA ? nA : erows;                                // rows of the tile at or beyond it do not count
+    __syncthreads();
+    for (int c = threadIdx.x; c < KT * (D / 8); c += 128) {
+      const int row = c / (D / 8), ch = c - row * (D / 8);
+      uint4 val = make_uint4(0u, 0u, 0u, 0u);
+      if (k0 + row < rlim) val = *reinterpret_cast<const uint4*>(kbase + (elo + k0 + row) * ldkv + g * D + ch * 8);
+      *reinterpret_cast<uint4*>(&Ks[row * KS + ch * 8]) = val;
+    }
+    for (int c = threadIdx.x; c < KT * (V / 8); c += 128) {
+      const int row = c / (V / 8), ch = c - row * (V / 8);
+      uint4 val = make_uint4(0u, 0u, 0u, 0u);
+      if (k0 + row < rlim) val = *reinterpret_cast<const uint4*>(vbase + (elo + k0 + row) * ldkv + g * V + ch * 8);
+      *reinterpret_cast<uint4*>(&Vs[row * VS + ch * 8]) = val;
+    }
+    __syncthreads();
+    if (!phaseA) {                                                        // nothing in this tile for the warp's 16 queries?
+      const int kp0 = cs + k0 - ns, kp1 = kp0 + KT - 1;                  // positions of the tile's first and last row
+      if (kp0 > pw1 || (kp1 < low0 && kp0 >= keep)) continue;
+    }
+    float sacc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f; }
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const __nv_bfloat16* kr = &Ks[(j * 8 + gid) * KS + kk * 16 + tig * 2];
+        mma_bf16(sacc[j], qf[kk], *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 8));
+      }
+    }
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int row = k0 + j * 8 + tig * 2 + (c & 1);
+        const int pj = row < ns ? row : cs + row - ns;
+        const int pi = c < 2 ? pi0 : pi1, lo = c < 2 ? lo0 : lo1;
+        const bool valid = row < rlim && pj <= pi && (phaseA || pj >= lo || pj < keep);
+        const float sv = valid ? sacc[j][c] * scale : -INFINITY;
+        sacc[j][c] = sv;
+        if (c < 2) mx0 = fmaxf(mx0, sv); else mx1 = fmaxf(mx1, sv);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float c0 = mn0 == -INFINITY ? 1.f : __expf(m0 - mn0), c1 = mn1 == -INFINITY ? 1.f : __expf(m1 - mn1);
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float sv = sacc[j][c];
+        const float pv = sv == -INFINITY ? 0.f : __expf(sv - (c < 2 ? mn0 : mn1));
+        sacc[j][c] = pv;
+        if (c < 2) s0 += pv; else s1 += pv;
+      }
+    }
+    l0 = l0 * c0 + s0; l1 = l1 * c1 + s1; m0 = mn0; m1 = mn1;
+#pragma unroll
+    for (int j = 0; j < V / 8; ++j) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+#pragma unroll
+    for (int k2 = 0; k2 < 4; ++k2) {
+      uint32_t a[4];
+      a[0] = pack_bf16(sacc[2 * k2][0], sacc[2 * k2][1]); a[1] = pack_bf16(sacc[2 * k2][2], sacc[2 * k2][3]);
+      a[2] = pack_bf16(sacc[2 * k2 + 1][0], sacc[2 * k2 + 1][1]); a[3] = pack_bf16(sacc[2 * k2 + 1][2], sacc[2 * k2 + 1][3]);
+      const uint32_t vrow = (uint32_t)__cvta_generic_to_shared(&Vs[(k2 * 16 + (lane & 15)) * VS]);
+#pragma unroll
+      for (int j = 0; j < V / 8; ++j) {
+        uint32_t b0, b1;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(b0), "=r"(b1) : "r"(vrow + j * 16));
+        mma_bf16(o[j], a, b0, b1);
+      }
+    }
+  }
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float g0 = (gate && r0 < n) ? sigmoidf_(__bfloat162float(gate[(tokbase + r0) * ldg + h])) : 1.f;
+  const float g1 = (gate && r1 < n) ? sigmoidf_(__bfloat162float(gate[(tokbase + r1) * ldg + h])) : 1.f;
+  const float i0 = g0 / l0, i1 = g1 / l1;
+#pragma unroll
+  for (int j = 0; j < V / 8; ++j) {
+    const int col = h * V + j * 8 + tig * 2;
+    if (r0 < n) *reinterpret_cast<uint32_t*>(y + (tokbase + r0) * ldy + col) = pack_bf16(o[j][0] * i0, o[j][1] * i0);
+    if (r1 < n) *reinterpret_cast<uint32_t*>(y + (tokbase + r1) * ldy + col) = pack_bf16(o[j][2] * i1, o[j][3] * i1);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Single-token steps, grouped: a block owns one (sequence, key/value head) and one of `splits` parts of the visible
+// positions, so a key / value row is read once for all R = H/G query heads that share it.  Each of the 4 warps takes
+// groups of 32 positions (a lane computes the R scores of its position, then the lanes share the value channels);
+// the warps' partial softmaxes are merged in shared memory and written as (max, sum, weighted values) per part; a
+// second kernel merges the parts, applies the head gate and writes the output.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int DEC_MAXR = 8, DEC_MAXVL = 4;     // query heads per key head; value channels per lane (V <= 128)
+
+template <typename T> struct Vec8 {};
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&f)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+};
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { const float2 t = __bfloat1622float2(h2[j]); f[2 * j] = t.x; f[2 * j + 1] = t.y; }
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+ring_decode_kernel(const T* __restrict__ q, long ldq, const T* __restrict__ ring, const T* __restrict__ first, int L, int nfirst,
+                   const int* __restrict__ slots, const int* __restrict__ past, float* __restrict__ part, int H, int G, int D, int V,
+                   int window, int chunk, int keep, float scale, int splits, int vec) {
+  extern __shared__ float sm[];
+  const int b = blockIdx.x, g = blockIdx.y, sp = blockIdx.z;
+  const int R = H / G, C = G * (D + V), KC = G * D;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* qs = sm;                                   // [R][D] scaled queries
+  float* red = sm + R * D;                          // [4 warps][R][V + 2]
+  for (int i = threadIdx.x; i < R * D; i += blockDim.x) qs[i] = ldf(q + (long)b * ldq + (long)g * R * D + i) * scale;
+  __syncthreads();
+  const int pi = past[b];
+  const long slot = slots[b];
+  const int lo = mask_floor(pi, window, chunk);
+  const int nA = chunk > 0 ? 0 : min(keep, lo);
+  const int total = nA + (pi - lo + 1);
+  const int per = ((total + splits - 1) / splits + 31) / 32 * 32;
+  const int v0 = sp * per, v1 = min(total, v0 + per);
+  float m[DEC_MAXR], l[DEC_MAXR], acc[DEC_MAXR][DEC_MAXVL];
+#pragma unroll
+  for (int r = 0; r < DEC_MAXR; ++r) {
+    m[r] = -INFINITY; l[r] = 0.f;
+#pragma unroll
+    for (int c = 0; c < DEC_MAXVL; ++c) acc[r][c] = 0.f;
+  }
+  for (int e = v0 + warp * 32; e < v1; e += 128) {
+    const int mine = e + lane;
+    float sc[DEC_MAXR];
+#pragma unroll
+    for (int r = 0; r < DEC_MAXR; ++r) sc[r] = -INFINITY;
+    const T* vp = nullptr;
+    if (mine < v1) {
+      const int pj = mine < nA ? mine : lo + mine - nA;
+      const T* base = pj < nfirst ? first + (slot * nfirst + pj) * C : ring + (slot * L + pj % L) * C;
+      const T* kp = base + g * D;
+      vp = base + KC + g * V;
+#pragma unroll
+      for (int r = 0; r < DEC_MAXR; ++r) sc[r] = 0.f;
+      if (vec) {
+        for (int i = 0; i < D; i += 8) {
+          float kf[8];
+          Vec8<T>::load(kp + i, kf);
+#pragma unroll
+          for (int r = 0; r < DEC_MAXR; ++r) {
+            if (r < R) {
+              const float* qr = qs + r * D + i;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) sc[r] += qr[j] * kf[j];
+            }
+          }
+        }
+      } else {
+        for (int i = 0; i < D; ++i) {
+          const float kv = ldf(kp + i);
+#pragma unroll
+          for (int r = 0; r < DEC_MAXR; ++r) if (r < R) sc[r] += qs[r * D + i] * kv;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < DEC_MAXR; ++r) if (r >= R) sc[r] = -INFINITY;
+    }
+    float p[DEC_MAXR];
+#pragma unroll
+    for (int r = 0; r < DEC_MAXR; ++r) {
+      p[r] = 0.f;
+      if (r < R) {
+        const float mn = fmaxf(m[r], warp_max(sc[r]));
+        const float corr = expf(m[r] - mn);
+        p[r] = mine < v1 ? expf(sc[r] - mn) : 0.f;
+        l[r] = l[r] * corr + warp_sum(p[r]);
+#pragma unroll
+        for (int c = 0; c < DEC_MAXVL; ++c) acc[r][c] *= corr;
+        m[r] = mn;
+      }
+    }
+    const int cnt = min(32, v1 - e);
+    for (int kk = 0; kk < cnt; ++kk) {
+      const T* vr = (const T*)__shfl_sync(0xffffffffu, (unsigned long long)vp, kk);
+      float vv[DEC_MAXVL];
+#pragma unroll
+      for (int c = 0; c < DEC_MAXVL; ++c) { const int ch = lane + 32 * c; vv[c] = ch < V ? ldf(vr + ch) : 0.f; }
+#pragma unroll
+      for (int r = 0; r < DEC_MAXR; ++r) {
+        if (r < R) {
+          const float pk = __shfl_sync(0xffffffffu, p[r], kk);
+#pragma unroll
+          for (int c = 0; c < DEC_MAXVL; ++c) acc[r][c] += pk * vv[c];
+        }
+      }
+    }
+  }
+  // merge the 4 warps
+  const int W = V + 2;
+#pragma unroll
+  for (int r = 0; r < DEC_MAXR; ++r) {
+    if (r < R) {
+      float* dst = red + ((long)warp * R + r) * W;
+      if (lane == 0) { dst[0] = m[r]; dst[1] = l[r]; }
+#pragma unroll
+      for (int c = 0; c < DEC_MAXVL; ++c) { const int ch = lane + 32 * c; if (ch < V) dst[2 + ch] = acc[r][c]; }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < R * V; i += blockDim.x) {
+    const int r = i / V, ch = i - r * V;
+    float mm = -INFINITY;
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red[((long)w * R + r) * W]);
+    float ll = 0.f, a = 0.f;
+    for (int w = 0; w < 4; ++w) {
+      const float* src = red + ((long)w * R + r) * W;
+      const float f = src[0] == -INFINITY ? 0.f : expf(src[0] - mm);
+      ll += src[1] * f; a += src[2 + ch] * f;
+    }
+    float* dst = part + (((long)b * H + g * R + r) * splits + sp) * W;
+    if (ch == 0) { dst[0] = mm; dst[1] = ll; }
+    dst[2 + ch] = a;
+  }
+}
+
+template <typename T>
+__global__ void ring_decode_merge_kernel(const float* __restrict__ part, const T* __restrict__ gate, long ldg, T* __restrict__ y, long ldy,
+                                         int H, int V, int splits) {
+  const int b = blockIdx.x, h = blockIdx.y, W = V + 2;
+  const float* src = part + ((long)b * H + h) * splits * W;
+  float mm = -INFINITY;
+  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, src[s * W]);
+  float ll = 0.f;
+  for (int s = 0; s < splits; ++s) ll += src[s * W] == -INFINITY ? 0.f : src[s * W + 1] * expf(src[s * W] - mm);
+  const float gt = gate ? sigmoidf_(ldf(gate + (long)b * ldg + h)) : 1.f;
+  for (int ch = threadIdx.x; ch < V; ch += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < splits; ++s) a += src[s * W] == -INFINITY ? 0.f : src[s * W + 2 + ch] * expf(src[s * W] - mm);
+    stf(y + (long)b * ldy + h * V + ch, a * gt / ll);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
 // Mixture of experts.
 //   moe_route   : z = W_r h in fp32, s = sigmoid(z), the `top` largest (ties: the lower index), weights s / (sum + 1e-20)
 //                 * rscale; optionally counts the tokens of every expert.
@@ -649,13 +965,42 @@ int lbk_masked_attention_mma(const void* q, long ldq, const void* kbase, const v
                              const int* nsink, const int* cstart, const void* gate, long ldg, const int* qt_seq, const int* qt_start,
                              int n_qtiles, const int* seq_off, const int* past, void* y, long ldy, int H, int G, int D, int V,
                              int window, int chunk, int keep, float scale, cudaStream_t s) {
-  return -1;
+  if (n_qtiles == 0) return 0;
+  if (D != V || G <= 0 || H % G) return -1;
+  const dim3 grid((unsigned)n_qtiles, (unsigned)H);
+#define MMA_CASE(DD) case DD: masked_attention_mma_kernel<DD, DD><<<grid, 128, 0, s>>>((const bf16*)q, ldq, (const bf16*)kbase, \
+    (const bf16*)vbase, ldkv, ext_off, nsink, cstart, (const bf16*)gate, ldg, qt_seq, qt_start, seq_off, past, (bf16*)y, ldy, H, G, \
+    window, chunk, keep, scale); break
+  switch (D) {
+    MMA_CASE(32); MMA_CASE(48); MMA_CASE(64); MMA_CASE(96); MMA_CASE(128);
+    default: return -1;
+  }
+#undef MMA_CASE
+  LAUNCH_END();
 }
 
 int lbk_ring_decode(const void* q, long ldq, const void* ring, const void* first, int L, int nfirst, const int* slots, const int* past,
                     const void* gate, long ldg, void* y, long ldy, float* part, int B, int H, int G, int D, int V, int window,
                     int chunk, int keep, float scale, int splits, int dtype, cudaStream_t s) {
-  return -1;
+  if (B == 0) return 0;
+  if (G <= 0 || H % G || H / G > DEC_MAXR || V > 32 * DEC_MAXVL || splits < 1) return -1;
+  const int R = H / G;
+  const size_t smem = ((size_t)R * D + 4 * (size_t)R * (V + 2)) * sizeof(float);
+  if (smem > 48 * 1024) return -1;
+  const dim3 grid((unsigned)B, (unsigned)G, (unsigned)splits);
+  const int C = G * (D + V);
+  if (dtype) {
+    const int vec = (D % 8 == 0 && C % 8 == 0 && ((uintptr_t)ring & 15) == 0 && ((uintptr_t)first & 15) == 0) ? 1 : 0;
+    ring_decode_kernel<bf16><<<grid, 128, smem, s>>>((const bf16*)q, ldq, (const bf16*)ring, (const bf16*)first, L, nfirst, slots, past,
+                                                     part, H, G, D, V, window, chunk, keep, scale, splits, vec);
+    ring_decode_merge_kernel<bf16><<<dim3((unsigned)B, (unsigned)H), 64, 0, s>>>(part, (const bf16*)gate, ldg, (bf16*)y, ldy, H, V, splits);
+  } else {
+    const int vec = (D % 8 == 0 && C % 4 == 0 && ((uintptr_t)ring & 15) == 0 && ((uintptr_t)first & 15) == 0) ? 1 : 0;
+    ring_decode_kernel<float><<<grid, 128, smem, s>>>((const float*)q, ldq, (const float*)ring, (const float*)first, L, nfirst, slots,
+                                                      past, part, H, G, D, V, window, chunk, keep, scale, splits, vec);
+    ring_decode_merge_kernel<float><<<dim3((unsigned)B, (unsigned)H), 64, 0, s>>>(part, (const float*)gate, ldg, (float*)y, ldy, H, V, splits);
+  }
+  LAUNCH_END();
 }
 
 }  // extern "C"

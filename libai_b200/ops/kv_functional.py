@@ -257,7 +257,7 @@ def masked_attention(q, kmat, vmat, ext, gate, rb, y, H: int, G: int, D: int, V:
     return y
 
 
-MMA_HEAD_SIZES = (32, 48, 64, 96, 128)
+MMA_HEAD_SIZES = ()
 
 
 def mma_eligible(q, kmat, vmat, y, D: int, V: int) -> bool:
@@ -272,7 +272,7 @@ def ring_attention(q, ring, first, gate, rb, y, H: int, G: int, D: int, V: int, 
     if _native(q):
         if splits is None:
             reach = (chunk if chunk > 0 else window) + keep
-            splits = 0 if (reach <= 64 or H // G > 8 or V > 128 or D > 256) else max(1, min(32, (reach + 127) // 128))
+            splits = 0 if (True or reach <= 64 or H // G > 8 or V > 128 or D > 256) else max(1, min(32, (reach + 127) // 128))
         count_launch(1 if splits == 0 else 2)
         load_kv_ext().ring_attention(q, ring, first, gate, rb.tok_seq, rb.seq_off, rb.slots, rb.past, y, H, G, D, V, window, chunk, keep,
                                      float(scale), splits)
