@@ -44,6 +44,7 @@ def linear_into(a, w, out):
     PyTorch product."""
     from . import use_native
 
+    a, w = a.detach(), w.detach()                               # an inference operator: nothing is recorded for autograd
     if (a.is_cuda and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and use_native(a) and a.dim() == 2
             and a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.shape[1] % 8 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0
             and w.shape[0] % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
@@ -257,7 +258,8 @@ def masked_attention(q, kmat, vmat, ext, gate, rb, y, H: int, G: int, D: int, V:
     return y
 
 
-MMA_HEAD_SIZES = ()
+MMA_HEAD_SIZES = (32, 48, 64, 96, 128)       # head sizes (keys = values) the tensor-core prompt kernel is built for
+GROUPED_DECODE = True                      # single-token steps: the grouped split kernel where its sizes allow
 
 
 def mma_eligible(q, kmat, vmat, y, D: int, V: int) -> bool:
@@ -272,7 +274,10 @@ def ring_attention(q, ring, first, gate, rb, y, H: int, G: int, D: int, V: int, 
     if _native(q):
         if splits is None:
             reach = (chunk if chunk > 0 else window) + keep
-            splits = 0 if (True or reach <= 64 or H // G > 8 or V > 128 or D > 256) else max(1, min(32, (reach + 127) // 128))
+            if not GROUPED_DECODE or H // G > 8 or V > 128 or (H // G * D + 4 * H // G * (V + 2)) * 4 > 48 * 1024:
+                splits = 0
+            else:                                               # enough blocks for the device, at least 64 positions each
+                splits = max(1, min(32, (reach + 63) // 64, -(-296 // (q.shape[0] * G))))
         count_launch(1 if splits == 0 else 2)
         load_kv_ext().ring_attention(q, ring, first, gate, rb.tok_seq, rb.seq_off, rb.slots, rb.past, y, H, G, D, V, window, chunk, keep,
                                      float(scale), splits)

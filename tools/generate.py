@@ -3,7 +3,7 @@
     python tools/generate.py --model DIR --prompts "5 17 3;9 9 12 40" --max-new-tokens 16 [--dtype float32] [--do-sample …]
 
 The model class and loader come from ``config.json`` (``libai_b200.models.utils.model_loader.auto``).  Models with per-sequence
-state (Bumodra) run through ``RequestScheduler.generate``: one ragged step for all prompts, then one token per live request;
+state (Bumodra, Nefelorn) run through ``RequestScheduler.generate``: one ragged step for all prompts, then one token per live request;
 the others through ``Generator.generate`` on a left-padded batch.  Prints one line of generated ids per prompt.
 """
 import argparse
@@ -32,9 +32,10 @@ def main(argv=None):
     device = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
     dtype = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32
     if device.startswith("cuda"):
+        from libai_b200.models.utils.model_loader.auto import native_libs_of
         from libai_b200.ops import build
 
-        build.build()
+        build.build(only=native_libs_of(a.model, dtype) + ["_C"])
     from libai_b200.models.utils.model_loader.auto import load_pretrained
 
     model = load_pretrained(a.model, dtype=dtype, device=device)
