@@ -16,6 +16,8 @@ int lb_gemm_bf16(const void* a, const void* b, void* out, int M, int N, int K, i
                  int epi, const void* bias, int act, void* pre_out, int force_bn, int force_splits, cudaStream_t s);
 int lb_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd, int rows, int H,
                 float eps, int rms, int dtype, int wdtype, cudaStream_t s);
+int lb_gemm_bf16_grouped(const void* a, const void* b, void* out, int M, int N, int K, int lda, int ldo, int epi,
+                         const int* tile_group, int groups, cudaStream_t stream);
 int lb_gemm_bf16_bias_residual(const void* x, const void* w, void* out, int M, int N, int K, int lda, int ldb,
                                const void* bias, const void* residual, cudaStream_t s);
 int lb_gemm_fp8(const void* xq, const void* wq, void* out, int M, int N, int K, const void* bias, int act, void* pre_out,
@@ -140,6 +142,50 @@ Tensor gemm(const Tensor& a, const Tensor& b, int64_t layout, const c10::optiona
                      (int)b.stride(0), (int)out.stride(0), (int)layout, epi, bias_ptr, 0, nullptr, 0, 0, cur_stream()),
         "gemm");
   return out;
+}
+
+// One product per group of consecutive rows: rows [sum(counts[:e]), +counts[e]) of `a` [P, K] times w[e] [N, K]ᵀ into the same rows
+// of `out` [P, N] (bf16 or fp32).  The group sizes are host numbers; the launches are issued back to back from here, which
+// is what the experts of a mixture-of-experts layer need once the rows are sorted by expert.
+void gemm_grouped(const Tensor& a, const Tensor& w, const std::vector<int64_t>& counts, Tensor out) {
+  TORCH_CHECK(a.is_cuda() && w.is_cuda() && out.is_cuda() && a.dim() == 2 && w.dim() == 3 && out.dim() == 2, "gemm_grouped: a [P,K], w [E,N,K], out [P,N]");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && a.stride(1) == 1 && w.is_contiguous() &&
+              out.stride(1) == 1, "gemm_grouped: bf16 row-major operands");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kFloat, "gemm_grouped: out must be bf16 or fp32");
+  const int64_t K = a.size(1), N = w.size(1), E = w.size(0);
+  TORCH_CHECK(w.size(2) == K && out.size(1) == N && out.size(0) == a.size(0) && (int64_t)counts.size() == E, "gemm_grouped: shapes");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int epi = out.scalar_type() == at::kBFloat16 ? 0 : 1;
+  const size_t esz = epi ? 4 : 2;
+  int64_t at = 0;
+  for (int64_t e = 0; e < E; ++e) {
+    const int64_t c = counts[e];
+    if (c <= 0) continue;
+    TORCH_CHECK(at + c <= a.size(0), "gemm_grouped: the counts exceed the rows");
+    check(lb_gemm_bf16((const char*)a.data_ptr() + at * a.stride(0) * 2, (const char*)w.data_ptr() + e * N * K * 2,
+                       (char*)out.data_ptr() + at * out.stride(0) * esz, (int)c, (int)N, (int)K, (int)a.stride(0), (int)K,
+                       (int)out.stride(0), 0, epi, nullptr, 0, nullptr, 0, 0, cur_stream()), "gemm_grouped");
+    at += c;
+  }
+}
+
+// The same as ONE launch with the groups known on the device only: `a` [M, K] with M a multiple of 128, every 128-row block
+// of it belongs to matrix tile_group[block] of `w` [E, N, K] (int32 on the device; < 0 = the block holds no rows and is
+// skipped).  No host synchronisation, so the call can be captured in a CUDA graph.
+void gemm_grouped_blocks(const Tensor& a, const Tensor& w, const Tensor& tile_group, Tensor out) {
+  TORCH_CHECK(a.is_cuda() && w.is_cuda() && out.is_cuda() && a.dim() == 2 && w.dim() == 3 && out.dim() == 2, "gemm_grouped_blocks: a [M,K], w [E,N,K], out [M,N]");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && a.stride(1) == 1 && w.is_contiguous() &&
+              out.stride(1) == 1, "gemm_grouped_blocks: bf16 row-major operands");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kFloat, "gemm_grouped_blocks: out must be bf16 or fp32");
+  const int64_t M = a.size(0), K = a.size(1), N = w.size(1), E = w.size(0);
+  TORCH_CHECK(w.size(2) == K && out.size(1) == N && out.size(0) == M && M % 128 == 0, "gemm_grouped_blocks: shapes (M a multiple of 128)");
+  TORCH_CHECK(tile_group.is_cuda() && tile_group.scalar_type() == at::kInt && tile_group.is_contiguous() && tile_group.numel() >= M / 128,
+              "gemm_grouped_blocks: int32 group of every 128-row block");
+  TORCH_CHECK(E * N < (int64_t)1 << 31, "gemm_grouped_blocks: stacked rows exceed the tensor map's range");
+  c10::cuda::CUDAGuard guard(a.device());
+  check(lb_gemm_bf16_grouped(a.data_ptr(), w.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, (int)a.stride(0), (int)out.stride(0),
+                             out.scalar_type() == at::kBFloat16 ? 0 : 1, tile_group.data_ptr<int>(), (int)E, cur_stream()),
+        "gemm_grouped_blocks");
 }
 
 // dpre = (gy @ w) * act'(pre): the dgrad GEMM of the layer that consumed act(pre), with the activation backward
@@ -787,6 +833,8 @@ TORCH_LIBRARY(libai_b200, m) {
   m.def("device_barrier(int[] flag_ptrs, int world, int rank, int slot, int epoch) -> ()", &device_barrier);
   m.def("p2p_allgather(Tensor shard, int[] out_ptrs, int[] flag_ptrs, Tensor(a!) done_counter, int world, int rank, int epoch) -> ()", &p2p_allgather);
   m.def("gemm(Tensor a, Tensor b, int layout, Tensor? bias, Tensor? out, bool accumulate, ScalarType out_dtype) -> Tensor", &gemm);
+  m.def("gemm_grouped(Tensor a, Tensor w, int[] counts, Tensor(a!) out) -> ()", &gemm_grouped);
+  m.def("gemm_grouped_blocks(Tensor a, Tensor w, Tensor tile_group, Tensor(a!) out) -> ()", &gemm_grouped_blocks);
   m.def("linear_bias_residual(Tensor x, Tensor w, Tensor? bias, Tensor residual) -> Tensor", &linear_bias_residual);
   m.def("embedding_fwd(Tensor ids, Tensor table, int vocab_start) -> Tensor", &embedding_fwd);
   m.def("embedding_bwd(Tensor ids, Tensor gy, Tensor(a!) grad, int vocab_start) -> ()", &embedding_bwd);

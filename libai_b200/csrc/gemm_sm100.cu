@@ -51,6 +51,10 @@ struct GemmParams {
   int fp8;
   const float* deq_a;         // per-tensor dequantisation scales (device scalars): out = acc * deq_a[0] * deq_b[0]
   const float* deq_b;
+  // grouped mode (NT layout, single-CTA tiles, no split-K): B is a stack of matrices [groups * N, K] and every BLOCK_M-row
+  // block of A belongs to one of them — tile_group[m_blk] = its group, < 0 = the block holds no rows (skipped by all
+  // roles alike).  The list lives in device memory, so the row counts of the groups never reach the host.
+  const int* tile_group;
 };
 
 // Fused collective modes (tensor parallel): peer pointers refer to NVLink peer-mapped symmetric memory.
@@ -386,6 +390,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         int split, mn;
         decode_tile(tile, mn, split);
         const int m_blk = map_m(mn / n_blocks) * CTAS + cta_rank, n_blk = mn % n_blocks;   // this CTA's 128-row block
+        int grp_row = 0;                                          // grouped mode: first row of this block's matrix in B
+        if (p.tile_group) {
+          const int grp = p.tile_group[m_blk];
+          if (grp < 0) continue;
+          grp_row = grp * p.N;
+        }
         // gathered A: rows of the local shard come straight from the shard's own tensor map, rows owned by a peer
         // from the gathered buffer once that peer's copy CTAs have pushed the row block (arrival counter)
         const bool a_local = cp.mode == COMM_AG && !ag_b && m_blk / mbpr == cp.rank;
@@ -395,7 +405,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         const CUtensorMap* map_a = a_local ? &tmap_g : &tmap_a;
         const int m_row = a_local ? (m_blk - cp.rank * mbpr) * BLOCK_M : m_blk * BLOCK_M;
-        const int n_row = n_blk * BLOCK_N + cta_rank * (BLOCK_N / CTAS);   // pair: this CTA's half of the B tile
+        const int n_row = grp_row + n_blk * BLOCK_N + cta_rank * (BLOCK_N / CTAS);   // pair: this CTA's half of the B tile
         const int kb0 = split * p.k_per_split;
         const int kb1 = min(kb0 + p.k_per_split, k_blocks_total);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -449,7 +459,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               tma_load_2d(sa + a * (BLOCK_K * 128), &tmap_a, &full_bar[stage], m_blk * BLOCK_M + a * 64, kb * BLOCK_K);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BLOCK_K, n_blk * BLOCK_N);
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BLOCK_K, grp_row + n_blk * BLOCK_N);
           } else {
 #pragma unroll
             for (int a = 0; a < BLOCK_N / 64; ++a)
@@ -473,6 +483,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     for (int tile = cta; tile < num_tiles && cta_rank == 0; tile += cta_stride) {   // (pair: the leader issues for both)
       int split, mn_unused;
       decode_tile(tile, mn_unused, split);
+      if (p.tile_group && p.tile_group[mn_unused / n_blocks] < 0) continue;   // grouped mode: an empty row block
       const int kb0 = split * p.k_per_split;
       const int kb1 = min(kb0 + p.k_per_split, k_blocks_total);
       mbar_wait(&tmem_empty[acc], acc_phase ^ 1);
@@ -538,6 +549,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int mn, split_unused;
       decode_tile(tile, mn, split_unused);
       const int m_blk = map_m(mn / n_blocks) * CTAS + cta_rank, n_blk = mn % n_blocks;   // this CTA's 128-row block
+      if (p.tile_group && p.tile_group[m_blk] < 0) continue;                  // grouped mode: an empty row block
       mbar_wait(&tmem_full[acc], acc_phase);
       tc_fence_after_sync();
       const int row = m_blk * BLOCK_M + quad * 32 + lane;
@@ -975,9 +987,10 @@ static int gemm_allow_2cta() {
 static int gemm_impl(const void* a, const void* b, void* out, int M, int N, int K, int lda, int ldb, int ldo, int layout,
                      int epi, const void* bias, int act, void* pre_out, const void* pre_in, int force_bn,
                      int force_splits, const lb::CommParams& cp_in, cudaStream_t stream, const float* deq_a = nullptr,
-                     const float* deq_b = nullptr, float* colsum = nullptr) {
+                     const float* deq_b = nullptr, float* colsum = nullptr, const int* tile_group = nullptr, int groups = 1) {
   lb::CommParams cp = cp_in;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (tile_group && (layout != 0 || epi == 2 || cp_in.mode != lb::COMM_NONE || deq_a || groups < 1)) return -8;
   if ((lda % 8) || (ldb % 8) || (N % 8) || (ldo % 4)) return -1;
   const bool a_mn = (layout == 2);
   const bool b_mn = (layout != 0);
@@ -999,7 +1012,7 @@ static int gemm_impl(const void* a, const void* b, void* out, int M, int N, int 
       // cost ~ waves * per-tile time (proportional to c, narrower tiles pay more shared-memory traffic per
       // flop, plus a fixed prologue/epilogue overhead per tile)
       double eff = c == 256 ? 1.0 : (c == 192 ? 1.03 : (c == 128 ? 1.08 : 1.2));
-      if (c == 256 && cp_in.mode == lb::COMM_NONE && deq_a == nullptr && M > lb::BLOCK_M && gemm_allow_2cta()) {
+      if (c == 256 && cp_in.mode == lb::COMM_NONE && deq_a == nullptr && M > lb::BLOCK_M && gemm_allow_2cta() && !tile_group) {
         // 256-wide tiles run on CTA pairs (256 x 256 per pair, half the B traffic per SM): measured ~12 % faster per
         // tile row, scheduled over sms / 2 pairs
         tiles = (long)((m_blocks + 1) / 2) * ((N + c - 1) / c);
@@ -1084,6 +1097,7 @@ static int gemm_impl(const void* a, const void* b, void* out, int M, int N, int 
   p.fp8 = (deq_a != nullptr && deq_b != nullptr) ? 1 : 0;
   p.deq_a = deq_a;
   p.deq_b = deq_b;
+  p.tile_group = tile_group;
 
   // CTA pairs (cta_group::2, 256 x 256 tiles, each CTA stages half of B) for the plain bf16 GEMMs whose tile width is
   // 256: 10-27 % faster than the single-CTA tiles on the benchmark shapes (8192^3 0.71 vs 0.81 ms, LM head 0.64 vs
@@ -1092,10 +1106,10 @@ static int gemm_impl(const void* a, const void* b, void* out, int M, int N, int 
   // (fused collectives: shards must hold whole 256-row pair tiles and the copy CTAs come in pairs)
   const bool comm_ok = cp.mode == lb::COMM_NONE ||
                        (cp.rows_per_rank % (2 * lb::BLOCK_M) == 0 && cp.n_comm % 2 == 0 && gemm_allow_2cta() >= 2);
-  const bool two_cta = allow_2cta && bn == 256 && comm_ok && !p.fp8 && M > lb::BLOCK_M;
+  const bool two_cta = allow_2cta && bn == 256 && comm_ok && !p.fp8 && M > lb::BLOCK_M && !tile_group;
   CUtensorMap ta, tb, tg;
   if (!operand_tmap(&ta, a, a_mn, M, K, lda, lb::BLOCK_M)) return -2;
-  if (!operand_tmap(&tb, b, b_mn, N, K, ldb, two_cta ? bn / 2 : bn)) return -2;
+  if (!operand_tmap(&tb, b, b_mn, tile_group ? N * groups : N, K, ldb, two_cta ? bn / 2 : bn)) return -2;
   tg = ta;
   if (cp.mode == lb::COMM_AG) {
     // tensor map of the local shard of the gathered operand: [rows_per_rank, K] rows of A (NT/NN), or rows_per_rank
@@ -1166,6 +1180,16 @@ extern "C" int lb_gemm_bf16(const void* a, const void* b, void* out, int M, int 
   memset(&cp, 0, sizeof(cp));
   return gemm_impl(a, b, out, M, N, K, lda, ldb, ldo, layout, epi, bias, act, pre_out, nullptr, force_bn, force_splits, cp,
                    stream);
+}
+
+// Grouped NT GEMM: out[M, N] rows of 128-row block m = a rows x (b[tile_group[m]] [N, K])ᵀ; blocks with tile_group < 0 are skipped.
+extern "C" int lb_gemm_bf16_grouped(const void* a, const void* b, void* out, int M, int N, int K, int lda, int ldo, int epi,
+                                    const int* tile_group, int groups, cudaStream_t stream) {
+  lb::CommParams cp;
+  memset(&cp, 0, sizeof(cp));
+  if (M % lb::BLOCK_M || !tile_group) return -8;
+  return gemm_impl(a, b, out, M, N, K, lda, K, ldo, 0, epi, nullptr, 0, nullptr, nullptr, 0, 0, cp, stream, nullptr, nullptr, nullptr,
+                   tile_group, groups);
 }
 
 // fp8 forward GEMM: y[M,N] (bf16) = act((xq[M,K] · wq[N,K]ᵀ) * deq_x * deq_w + bias); xq / wq hold E4M3 bytes, K % 16 == 0.

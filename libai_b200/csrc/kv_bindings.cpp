@@ -33,12 +33,12 @@ int lbk_masked_attention_mma(const void* q, long ldq, const void* kbase, const v
 int lbk_ring_decode(const void* q, long ldq, const void* ring, const void* first, int L, int nfirst, const int* slots, const int* past,
                     const void* gate, long ldg, void* y, long ldy, float* part, int B, int H, int G, int D, int V, int window,
                     int chunk, int keep, float scale, int splits, int dtype, cudaStream_t s);
-int lbk_moe_route(const void* h, long ldh, const void* wr, int E, int n, int top, float rscale, int* idx, float* wts, int* counts,
-                  long tokens, int dtype, cudaStream_t s);
+int lbk_moe_topk(const float* z, long ldz, int E, int top, float rscale, int* idx, float* wts, int* counts, long tokens,
+                 cudaStream_t s);
 int lbk_moe_pairs(const void* h, long ldh, const void* wgu, const void* wd, const int* idx, const float* wts, void* a, float* out,
                   long tokens, int ff, int n, int top, int act, int dtype, cudaStream_t s);
 int lbk_moe_sort(const void* h, long ldh, const int* idx, const int* counts, int* offsets, int* cursor, int* pos, void* xs, long tokens,
-                 int E, int n, int top, int dtype, cudaStream_t s);
+                 int E, int n, int top, int align, int* tile_group, int tiles, int dtype, cudaStream_t s);
 }
 
 namespace {
@@ -228,16 +228,16 @@ void ring_attention(const Tensor& q, const Tensor& ring, const Tensor& first, co
                              (int)keep, (float)scale, dtype, cur_stream()), "ring_attention");
 }
 
-void moe_route(const Tensor& h, const Tensor& wr, int64_t top, double rscale, Tensor idx, Tensor wts, const OptT& counts) {
-  rows2d(h, "moe_route h");
-  TORCH_CHECK(wr.is_cuda() && wr.dim() == 2 && wr.is_contiguous() && wr.size(1) == h.size(1) && code(wr) == code(h), "moe_route: router [E, width]");
-  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kInt && idx.is_contiguous() && idx.numel() == h.size(0) * top, "moe_route: idx int32 [tokens, top]");
-  TORCH_CHECK(wts.is_cuda() && wts.scalar_type() == at::kFloat && wts.is_contiguous() && wts.numel() == h.size(0) * top, "moe_route: weights fp32 [tokens, top]");
+void moe_topk(const Tensor& z, int64_t top, double rscale, Tensor idx, Tensor wts, const OptT& counts) {
+  rows2d(z, "moe_topk z");
+  TORCH_CHECK(z.scalar_type() == at::kFloat, "moe_topk: fp32 router logits expected");
+  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kInt && idx.is_contiguous() && idx.numel() == z.size(0) * top, "moe_topk: idx int32 [tokens, top]");
+  TORCH_CHECK(wts.is_cuda() && wts.scalar_type() == at::kFloat && wts.is_contiguous() && wts.numel() == z.size(0) * top, "moe_topk: weights fp32 [tokens, top]");
   int* cp = nullptr;
-  if (has(counts)) { TORCH_CHECK(counts->is_cuda() && counts->scalar_type() == at::kInt && counts->numel() >= wr.size(0), "moe_route: counts"); cp = counts->data_ptr<int>(); }
-  c10::cuda::CUDAGuard guard(h.device());
-  check(lbk_moe_route(h.data_ptr(), h.stride(0), wr.data_ptr(), (int)wr.size(0), (int)h.size(1), (int)top, (float)rscale, idx.data_ptr<int>(),
-                      wts.data_ptr<float>(), cp, h.size(0), code(h), cur_stream()), "moe_route");
+  if (has(counts)) { TORCH_CHECK(counts->is_cuda() && counts->scalar_type() == at::kInt && counts->numel() >= z.size(1), "moe_topk: counts"); cp = counts->data_ptr<int>(); }
+  c10::cuda::CUDAGuard guard(z.device());
+  check(lbk_moe_topk(z.data_ptr<float>(), z.stride(0), (int)z.size(1), (int)top, (float)rscale, idx.data_ptr<int>(), wts.data_ptr<float>(), cp,
+                     z.size(0), cur_stream()), "moe_topk");
 }
 
 void moe_pairs(const Tensor& h, const Tensor& wgu, const Tensor& wd, const Tensor& idx, const Tensor& wts, Tensor a, Tensor out, int64_t act) {
@@ -254,14 +254,23 @@ void moe_pairs(const Tensor& h, const Tensor& wgu, const Tensor& wd, const Tenso
                       tokens, (int)ff, (int)n, (int)top, (int)act, code(h), cur_stream()), "moe_pairs");
 }
 
-void moe_sort(const Tensor& h, const Tensor& idx, const Tensor& counts, Tensor offsets, Tensor cursor, Tensor pos, Tensor xs) {
+// rows sorted by expert; with `tile_group` (int32 [rows of xs / align]) every expert's range starts on a multiple of `align`
+void moe_sort(const Tensor& h, const Tensor& idx, const Tensor& counts, Tensor offsets, Tensor cursor, Tensor pos, Tensor xs, int64_t align,
+              const OptT& tile_group) {
   rows2d(h, "moe_sort h");
   const int64_t tokens = h.size(0), n = h.size(1), top = idx.numel() / std::max<int64_t>(tokens, 1), E = counts.numel();
   TORCH_CHECK(offsets.numel() == E + 1 && cursor.numel() >= E && pos.numel() == idx.numel(), "moe_sort: metadata sizes");
-  TORCH_CHECK(xs.is_cuda() && xs.dim() == 2 && xs.is_contiguous() && xs.size(0) == tokens * top && xs.size(1) == n && code(xs) == code(h), "moe_sort: xs [tokens*top, width]");
+  TORCH_CHECK(xs.is_cuda() && xs.dim() == 2 && xs.is_contiguous() && xs.size(1) == n && code(xs) == code(h) &&
+              xs.size(0) >= tokens * top + E * (align - 1), "moe_sort: xs [tokens*top (+ padding), width]");
+  int* tg = nullptr; int tiles = 0;
+  if (has(tile_group)) {
+    TORCH_CHECK(align > 1 && xs.size(0) % align == 0 && tile_group->numel() == xs.size(0) / align, "moe_sort: one group entry per aligned block of xs");
+    tg = const_cast<int*>(meta(*tile_group)); tiles = (int)tile_group->numel();
+  }
   c10::cuda::CUDAGuard guard(h.device());
   check(lbk_moe_sort(h.data_ptr(), h.stride(0), meta(idx), meta(counts), const_cast<int*>(meta(offsets)), const_cast<int*>(meta(cursor)),
-                     const_cast<int*>(meta(pos)), xs.data_ptr(), tokens, (int)E, (int)n, (int)top, code(h), cur_stream()), "moe_sort");
+                     const_cast<int*>(meta(pos)), xs.data_ptr(), tokens, (int)E, (int)n, (int)top, (int)align, tg, tiles, code(h), cur_stream()),
+        "moe_sort");
 }
 
 }  // namespace
@@ -276,7 +285,7 @@ TORCH_LIBRARY(libai_b200_kv, m) {
   m.def("kv_gather(Tensor ring, Tensor first, Tensor knew, Tensor vnew, Tensor ext_seq, Tensor ext_off, Tensor nsink, Tensor cstart, Tensor seq_off, Tensor slots, Tensor past, Tensor(a!) ext) -> ()", &kv_gather);
   m.def("masked_attention(Tensor q, Tensor kmat, Tensor vmat, Tensor ext_off, Tensor nsink, Tensor cstart, Tensor? gate, Tensor tok_seq, Tensor seq_off, Tensor past, Tensor? qt_seq, Tensor? qt_start, Tensor(a!) y, int H, int G, int D, int V, int window, int chunk, int keep, float scale) -> ()", &masked_attention);
   m.def("ring_attention(Tensor q, Tensor ring, Tensor first, Tensor? gate, Tensor tok_seq, Tensor seq_off, Tensor slots, Tensor past, Tensor(a!) y, int H, int G, int D, int V, int window, int chunk, int keep, float scale, int splits) -> ()", &ring_attention);
-  m.def("moe_route(Tensor h, Tensor wr, int top, float rscale, Tensor(a!) idx, Tensor(b!) wts, Tensor(c!)? counts) -> ()", &moe_route);
+  m.def("moe_topk(Tensor z, int top, float rscale, Tensor(a!) idx, Tensor(b!) wts, Tensor(c!)? counts) -> ()", &moe_topk);
   m.def("moe_pairs(Tensor h, Tensor wgu, Tensor wd, Tensor idx, Tensor wts, Tensor(a!) a, Tensor(b!) out, int act) -> ()", &moe_pairs);
-  m.def("moe_sort(Tensor h, Tensor idx, Tensor counts, Tensor(a!) offsets, Tensor(b!) cursor, Tensor(c!) pos, Tensor(d!) xs) -> ()", &moe_sort);
+  m.def("moe_sort(Tensor h, Tensor idx, Tensor counts, Tensor(a!) offsets, Tensor(b!) cursor, Tensor(c!) pos, Tensor(d!) xs, int align, Tensor(e!)? tile_group) -> ()", &moe_sort);
 }

@@ -154,6 +154,31 @@ __global__ void act_rows_kernel(const T* __restrict__ in, long ldi, T* __restric
   }
 }
 
+// bf16, 8 channels per thread with 16-byte accesses (n a multiple of 8, rows 16-byte aligned)
+__global__ void act_rows_vec8_kernel(const __nv_bfloat16* __restrict__ in, long ldi, __nv_bfloat16* __restrict__ out, long ldo, long rows,
+                                     int n, int act, int gated) {
+  const int per = n / 8;
+  const long total = rows * per;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / per; const int c = (int)(i - r * per) * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(in + r * ldi + c);
+    uint4 b = make_uint4(0u, 0u, 0u, 0u);
+    if (gated) b = *reinterpret_cast<const uint4*>(in + r * ldi + n + c);
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 v = __bfloat1622float2(a2[j]);
+      v.x = act_apply(v.x, act); v.y = act_apply(v.y, act);
+      if (gated) { const float2 u = __bfloat1622float2(b2[j]); v.x *= u.x; v.y *= u.y; }
+      o2[j] = __floats2bfloat162_rn(v.x, v.y);
+    }
+    *reinterpret_cast<uint4*>(out + r * ldo + c) = o;
+  }
+}
+
 __global__ void softcap_kernel(float* __restrict__ l, float cap, long total) {
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x)
     l[i] = cap * tanhf(l[i] / cap);
@@ -692,29 +717,23 @@ __global__ void ring_decode_merge_kernel(const float* __restrict__ part, const T
 
 // ------------------------------------------------------------------------------------------------------------------
 // Mixture of experts.
-//   moe_route   : z = W_r h in fp32, s = sigmoid(z), the `top` largest (ties: the lower index), weights s / (sum + 1e-20)
-//                 * rscale; optionally counts the tokens of every expert.
+//   moe_topk    : from the fp32 router logits z = W_r h (a product of the caller's): s = sigmoid(z), the `top` largest
+//                 (ties: the lower index), weights s / (sum + 1e-20) * rscale; optionally counts the tokens of every expert.
 //   pair kernels: few tokens (single-token steps): every (token, chosen expert) pair reads its expert's matrices —
 //                 a = act(W_gate h) * (W_up h), then out[t] = sum_k weight_k W_down,k a_k in fp32.
 //   sort kernels: many tokens: rows are copied into a matrix sorted by expert (offsets from the counts), the experts
 //                 run as dense products on their row ranges, and the fused residual kernel gathers the weighted sum.
 // Expert matrices are stacked: wgu [E, 2*ff, n] (gate rows, then up rows), wd [E, n, ff].
 // ------------------------------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ wr, int E, int n, int top, float rscale,
-                                 int* __restrict__ idx, float* __restrict__ wts, int* __restrict__ counts, long tokens) {
+// one warp per token over its fp32 router logits z [tokens, E]
+__global__ void moe_topk_kernel(const float* __restrict__ z, long ldz, int E, int top, float rscale, int* __restrict__ idx,
+                                float* __restrict__ wts, int* __restrict__ counts, long tokens) {
   extern __shared__ float sm[];
   const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const long tok = (long)blockIdx.x * nw + wib;
-  float* hs = sm + (long)wib * (n + E);
-  float* sc = hs + n;
+  float* sc = sm + (long)wib * E;
   if (tok >= tokens) return;                     // warps are independent below
-  for (int i = lane; i < n; i += 32) hs[i] = ldf(h + tok * ldh + i);
-  __syncwarp();
-  for (int e = 0; e < E; ++e) {
-    const float z = warp_dot<T>(wr + (long)e * n, hs, n, lane);
-    if (lane == 0) sc[e] = sigmoidf_(z);
-  }
+  for (int e = lane; e < E; e += 32) sc[e] = sigmoidf_(z[tok * ldz + e]);
   __syncwarp();
   float sum = 0.f, mine_w = 0.f; int mine_e = 0;
   for (int k = 0; k < top; ++k) {
@@ -785,12 +804,28 @@ moe_pair_down_kernel(const T* __restrict__ a, const T* __restrict__ wd, const in
   }
 }
 
-// offsets[e] = first sorted row of expert e (offsets[E] = all pairs); the per-expert cursors start at zero
-__global__ void moe_offsets_kernel(const int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ cursor, int E) {
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
+// offsets[e] = first sorted row of expert e (offsets[E] = end of the last one); the per-expert cursors start at zero.
+// With `align` > 1 every expert's range starts on a multiple of it, and tile_group[i] names the expert that owns rows
+// [i*align, (i+1)*align) of the sorted matrix (-1: nobody; `tiles` entries) — the list a grouped GEMM schedules by.
+__global__ void moe_offsets_kernel(const int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ cursor, int E, int align,
+                                   int* __restrict__ tile_group, int tiles) {
+  __shared__ int s_off[1025];
+  if (threadIdx.x == 0) {
     int at = 0;
-    for (int e = 0; e < E; ++e) { offsets[e] = at; at += counts[e]; cursor[e] = 0; }
-    offsets[E] = at;
+    for (int e = 0; e < E; ++e) {
+      offsets[e] = at; s_off[e] = at; cursor[e] = 0;
+      at += (counts[e] + align - 1) / align * align;
+    }
+    offsets[E] = at; s_off[E] = at;
+  }
+  __syncthreads();
+  if (tile_group) {
+    for (int i = threadIdx.x; i < tiles; i += blockDim.x) {
+      const int row = i * align;
+      int g = -1;
+      for (int e = 0; e < E; ++e) if (row >= s_off[e] && row < s_off[e] + counts[e]) { g = e; break; }
+      tile_group[i] = g;
+    }
   }
 }
 
@@ -843,6 +878,12 @@ int lbk_dyt_residual(float* x, const void* y, long ldy, int ydtype, const int* p
 int lbk_act_rows(const void* in, long ldi, void* out, long ldo, long rows, int n, int act, int gated, int dtype, cudaStream_t s) {
   if (rows == 0 || n == 0) return 0;
   const long total = rows * n;
+  if (dtype && n % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    const long work = total / 8;
+    const unsigned g8 = (unsigned)((work + 255) / 256 > 148 * 16 ? 148 * 16 : (work + 255) / 256);
+    act_rows_vec8_kernel<<<g8, 256, 0, s>>>((const bf16*)in, ldi, (bf16*)out, ldo, rows, n, act, gated);
+    LAUNCH_END();
+  }
   const unsigned grid = (unsigned)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
   if (dtype) act_rows_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)in, ldi, (bf16*)out, ldo, rows, n, act, gated);
   else act_rows_kernel<float><<<grid, 256, 0, s>>>((const float*)in, ldi, (float*)out, ldo, rows, n, act, gated);
@@ -909,22 +950,13 @@ int lbk_masked_attention(const void* q, long ldq, const void* kbase, const void*
   LAUNCH_END();
 }
 
-int lbk_moe_route(const void* h, long ldh, const void* wr, int E, int n, int top, float rscale, int* idx, float* wts, int* counts,
-                  long tokens, int dtype, cudaStream_t s) {
+int lbk_moe_topk(const float* z, long ldz, int E, int top, float rscale, int* idx, float* wts, int* counts, long tokens,
+                 cudaStream_t s) {
   if (tokens == 0) return 0;
-  if (top > E) return -1;
-  int warps = 4;
-  while (warps > 1 && (size_t)warps * (n + E) * sizeof(float) > 96 * 1024) warps >>= 1;
-  const size_t smem = (size_t)warps * (n + E) * sizeof(float);
-  if (smem > 200 * 1024) return -1;
-  const unsigned grid = (unsigned)((tokens + warps - 1) / warps);
-  if (dtype) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    moe_route_kernel<bf16><<<grid, warps * 32, smem, s>>>((const bf16*)h, ldh, (const bf16*)wr, E, n, top, rscale, idx, wts, counts, tokens);
-  } else {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    moe_route_kernel<float><<<grid, warps * 32, smem, s>>>((const float*)h, ldh, (const float*)wr, E, n, top, rscale, idx, wts, counts, tokens);
-  }
+  if (top > E || (size_t)E * sizeof(float) > 12 * 1024) return -1;
+  const int warps = 4;
+  moe_topk_kernel<<<(unsigned)((tokens + warps - 1) / warps), warps * 32, (size_t)warps * E * sizeof(float), s>>>(z, ldz, E, top, rscale,
+                                                                                                               idx, wts, counts, tokens);
   LAUNCH_END();
 }
 
@@ -952,9 +984,10 @@ int lbk_moe_pairs(const void* h, long ldh, const void* wgu, const void* wd, cons
 }
 
 int lbk_moe_sort(const void* h, long ldh, const int* idx, const int* counts, int* offsets, int* cursor, int* pos, void* xs, long tokens,
-                 int E, int n, int top, int dtype, cudaStream_t s) {
+                 int E, int n, int top, int align, int* tile_group, int tiles, int dtype, cudaStream_t s) {
   if (tokens == 0) return 0;
-  moe_offsets_kernel<<<1, 32, 0, s>>>(counts, offsets, cursor, E);
+  if (E > 1024 || align < 1) return -1;
+  moe_offsets_kernel<<<1, 256, 0, s>>>(counts, offsets, cursor, E, align, tile_group, tiles);
   const unsigned pairs = (unsigned)(tokens * top);
   if (dtype) moe_scatter_kernel<bf16><<<pairs, 128, 0, s>>>((const bf16*)h, ldh, idx, offsets, cursor, pos, (bf16*)xs, n, top);
   else moe_scatter_kernel<float><<<pairs, 128, 0, s>>>((const float*)h, ldh, idx, offsets, cursor, pos, (float*)xs, n, top);

@@ -1,6 +1,8 @@
-"""Prefill / decode throughput of the stateful sequence-mixer model (Bumodra) beside Llama at equal width, depth and
-feed-forward size, random weights, one GPU.  ``bench.py --serving`` prints the result as one JSON line; ``--serving-kernels``
-adds device times of the individual kernels of one block at the same sizes with their roofline fractions.
+"""Prefill / decode throughput of the stateful models (Bumodra: delta-rule and latent-attention mixers; Nefelorn: ring-cached
+attention with chunk / kept-first window masks and mixture-of-experts feed-forwards) beside Llama at equal width, depth and
+(active) feed-forward size, random weights, one GPU.  ``bench.py --serving [--serving-model nefelorn]`` prints the result as
+one JSON line; ``--serving-kernels`` adds device times of the individual kernels of one block at the same sizes with their
+roofline fractions.
 
 Timing: CUDA events on the launching stream after warm-up steps, a synchronize on both sides, an L2 flush (a write larger
 than L2) between timed iterations of the kernel table.
@@ -191,11 +193,212 @@ def kernel_table(s, batch, prompt):
     return {"peaks": src, "hbm_bytes_per_s": hbm, "bf16_flops": flops, "rows": rows}
 
 
+# ======================================================================================================================
+# Nefelorn beside Llama
+# ======================================================================================================================
+NEFELORN_SIZES = {
+    # heads × dim with grouped keys, mask reach, experts (top of them active; top · expert_ff = Llama's intermediate size)
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, reach=512, keep=4, ff=4096, experts=16, top=2, expert_ff=1408,
+                  blocks=4, vocab=32000),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, reach=1024, keep=4, ff=8192, experts=32, top=2, expert_ff=2816,
+                  blocks=4, vocab=32000),
+}
+
+
+def nefelorn_config(s):
+    D = s["dim"]
+    moe = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "router": {"experts": s["experts"], "top": s["top"], "scale": 1.0}}
+
+    def chunked(mlp, kv_from=None):
+        m = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": D, "vdim": D, "mask": {"size": s["reach"]}, "scale": D ** -0.5,
+             "rot": {"dims": D, "base": 500000.0, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "attention", "mixer": m, "mlp": mlp}
+
+    def windowed(mlp):
+        return {"type": "attention_2", "mlp": mlp,
+                "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": D, "vdim": D, "scale": D ** -0.5,
+                          "mask": {"size": s["reach"], "keep_first": s["keep"]}, "rot": {"dims": D // 2, "base": 10000.0}}}
+
+    kinds = [chunked({"kind": "dense", "ff": s["ff"]}), windowed(moe), chunked(moe, kv_from=0), windowed(moe)]
+    layers = []
+    for i in range(s["blocks"]):
+        lc = json.loads(json.dumps(kinds[i % 4]))
+        if "kv_from" in lc["mixer"]:
+            lc["mixer"]["kv_from"] = i - 2
+        layers.append(lc)
+    return dict(vocab=s["vocab"], width=s["width"], norm={"eps": 1e-6}, embedding={"scale": s["width"] ** 0.5}, logit_softcap=30.0,
+                layers=layers)
+
+
+def build_nefelorn_and_llama(s, device="cuda"):
+    from libai_b200.config import DictConfig
+    from libai_b200.layers._param import param_defaults
+    from libai_b200.models import LlamaForCausalLM, NefelornForCausalLM
+
+    with param_defaults(dtype=torch.bfloat16, device=device, seed=1):
+        nef = NefelornForCausalLM(DictConfig(nefelorn_config(s))).eval()
+        llama = LlamaForCausalLM(DictConfig(dict(
+            hidden_layers=s["blocks"], vocab_size=s["vocab"], hidden_size=s["width"], intermediate_size=s["top"] * s["expert_ff"],
+            num_attention_heads=s["heads"], max_position_embeddings=8192, rms_norm_eps=1e-6, initializer_range=0.02,
+            use_scaled_init_for_output_weights=True, scale_mask_softmax_fusion=False, amp_enabled=False))).eval()
+    return nef.cuda(), llama.cuda()
+
+
+@torch.no_grad()
+def throughput_nefelorn(s, batch, prompt, new_tokens, steps, warmup):
+    from libai_b200.inference.scheduler import RequestScheduler
+
+    nef, llama = build_nefelorn_and_llama(s)
+    gen = torch.Generator().manual_seed(0)
+    ids = torch.randint(1, s["vocab"], (batch, prompt), generator=gen)
+    out = {}
+    sched = RequestScheduler(nef)
+    prompts = [row.tolist() for row in ids]
+
+    def prefill():
+        sched.step([(("p", i), p, [len(p) - 1]) for i, p in enumerate(prompts)])
+        sched.finish([("p", i) for i in range(batch)])
+
+    out["nefelorn_prefill_ms"] = _time(prefill, warmup, steps)
+    sched.step([(("d", i), p, []) for i, p in enumerate(prompts)])
+    entries = [(("d", i), [7], [0]) for i in range(batch)]
+    out["nefelorn_decode_ms"] = _time(lambda: sched.step(entries), warmup, new_tokens)
+    sched.cuda_graphs = False
+    out["nefelorn_decode_eager_ms"] = _time(lambda: sched.step(entries), warmup, new_tokens)
+    sched.finish([("d", i) for i in range(batch)])
+    dev_ids = ids.cuda()
+    out["llama_prefill_ms"] = _time(lambda: llama(dev_ids), warmup, steps)
+    a, d = llama.model.layers[0].self_attn.local_heads, llama.model.layers[0].self_attn.head_size
+    one = dev_ids[:, :1].contiguous()
+    llama.set_cache([(torch.randn(batch, a, prompt, d, device="cuda").to(torch.bfloat16),
+                      torch.randn(batch, a, prompt, d, device="cuda").to(torch.bfloat16)) for _ in range(s["blocks"])])
+    out["llama_decode_ms"] = _time(lambda: llama(one, use_cache=True), warmup, new_tokens)
+    llama.set_cache(None)
+    for name in ("nefelorn", "llama"):
+        out[f"{name}_prefill_tokens_per_s"] = batch * prompt / out[f"{name}_prefill_ms"] * 1e3
+        out[f"{name}_decode_tokens_per_s"] = batch / out[f"{name}_decode_ms"] * 1e3
+    out["params_nefelorn"] = sum(p.numel() for p in nef.parameters())
+    out["params_llama"] = sum(p.numel() for p in llama.parameters())
+    return out
+
+
+@torch.no_grad()
+def kernel_table_nefelorn(s, batch, prompt):
+    """Device time of every kernel of a Nefelorn block at these sizes (prefill rows = batch·prompt; decode rows = batch) beside
+    the like kernel of Llama, with the bytes / FLOPs the operation needs and the fraction of the measured roofline."""
+    from libai_b200.config import DictConfig
+    from libai_b200.inference.ragged import RaggedBatch
+    from libai_b200.layers import DynamicTanh, MoEFeedForward
+    from libai_b200.layers._param import param_defaults
+    from libai_b200.models.llama_model import LlamaMLP
+    from libai_b200.ops import functional as OF
+    from libai_b200.ops import kv_functional as KF
+
+    hbm, flops, src = _peaks()
+    dev, bf = "cuda", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    n, H, G, D, R, keep = s["width"], s["heads"], s["kv_heads"], s["dim"], s["reach"], s["keep"]
+    E, top, ff = s["experts"], s["top"], s["expert_ff"]
+    C = G * 2 * D
+    rows = []
+
+    def add(name, ms, bytes_=0.0, fl=0.0):
+        ideal = max(bytes_ / hbm, fl / flops) * 1e3
+        rows.append(dict(kernel=name, ms=round(ms, 4), ideal_ms=round(ideal, 5), roofline_fraction=round(ideal / ms, 4),
+                         bound="memory" if bytes_ / hbm >= fl / flops else "tensor"))
+
+    with param_defaults(dtype=bf, device=dev, seed=2):
+        na, nb = DynamicTanh(n), DynamicTanh(n)
+        moe = MoEFeedForward(n, ff, E, top)
+        lmlp = LlamaMLP(n, top * ff)
+    freq, ms_ = KF.rotary_frequencies(D, 5e5, {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0})
+    freq = freq.to(dev)
+    for phase, lens, past in (("prefill", [prompt] * batch, [0] * batch), ("decode", [1] * batch, [prompt] * batch)):
+        rb = RaggedBatch(lens, list(range(batch)), past, dev)
+        T = rb.tokens
+        x, y32 = torch.randn(T, n, device=dev), torch.randn(T, n, device=dev)
+        h = torch.empty(T, n, dtype=bf, device=dev)
+        add(f"{phase}: closing norm + residual + opening norm (Dynamic Tanh)",
+            _time(lambda: KF.dyt_residual(x, y32, post=na.triple(), nxt=nb.triple(), h=h), flush=flush), T * n * 14)
+        xb = torch.randn(T, n, device=dev).to(bf)
+        w = torch.ones(n, dtype=bf, device=dev)
+        add(f"{phase}: Llama RMS norm", _time(lambda: OF.rms_norm(xb, w, 1e-6), flush=flush), T * n * 4)
+        q = torch.randn(T, H * D, device=dev).to(bf)
+        kv = torch.randn(T, C, device=dev).to(bf)
+        qw, kw = torch.ones(H * D, dtype=bf, device=dev), torch.ones(G * D, dtype=bf, device=dev)
+        add(f"{phase}: query/key norm + rotation (whole-projection norm)",
+            _time(lambda: KF.qk_prepare(q, kv[:, :G * D], qw, kw, freq, ms_, rb, H, G, D, 1e-6, True, False), flush=flush), T * (H + G) * D * 4)
+        ring = torch.randn(batch, R, C, device=dev).to(bf)
+        first = torch.randn(batch, keep, C, device=dev).to(bf)
+        add(f"{phase}: cache write", _time(lambda: KF.kv_write(ring, first, kv[:, :G * D], kv[:, G * D:], rb), flush=flush),
+            min(T, batch * R) * C * 4)
+        gate = torch.randn(T, H, device=dev).to(bf)
+        yb = torch.empty(T, H * D, dtype=bf, device=dev)
+        if phase == "prefill":
+            ext = rb.kv_ext([(R, 0, keep)])
+            pairs = sum(min(t + 1, R) + (min(keep, t + 1 - R) if t + 1 > R else 0) for t in range(prompt)) * batch
+            add("prefill: sliding-window + kept-first attention (mma.sync)",
+                _time(lambda: KF.masked_attention(q, kv[:, :G * D], kv[:, G * D:], ext, None, rb, yb, H, G, D, D, R, 0, keep, D ** -0.5), flush=flush),
+                T * H * D * 4 + T * C * 2, pairs * H * D * 4.0)
+            ext2 = rb.kv_ext([(0, R, 0)])
+            pairs2 = sum(t % R + 1 for t in range(prompt)) * batch
+            add("prefill: chunked attention with head gate (mma.sync)",
+                _time(lambda: KF.masked_attention(q, kv[:, :G * D], kv[:, G * D:], ext2, gate, rb, yb, H, G, D, D, 0, R, 0, D ** -0.5), flush=flush),
+                T * H * D * 4 + T * C * 2, pairs2 * H * D * 4.0)
+            qkv4 = torch.randn(batch, prompt, H, 3 * D, device=dev).to(bf)
+            add("prefill: Llama causal flash attention (tcgen05; same heads, full context)",
+                _time(lambda: OF.attention_qkvpacked(qkv4, causal=True, scale=D ** -0.5), flush=flush),
+                qkv4.numel() * 2 + T * H * D * 2, batch * prompt * (prompt + 1) / 2 * H * D * 4.0)
+        else:
+            add("decode: grouped ring attention (window + kept-first)",
+                _time(lambda: KF.ring_attention(q, ring, first, None, rb, yb, H, G, D, D, R, 0, keep, D ** -0.5), flush=flush),
+                batch * (min(prompt + 1, R) + keep) * C * 2)
+            add("decode: one-warp-per-head ring attention (the generic kernel)",
+                _time(lambda: KF.ring_attention(q, ring, first, None, rb, yb, H, G, D, D, R, 0, keep, D ** -0.5, splits=0), flush=flush),
+                batch * (min(prompt + 1, R) + keep) * C * 2)
+            k = torch.randn(batch, H, prompt, D, device=dev).to(bf)
+            v = torch.randn(batch, H, prompt, D, device=dev).to(bf)
+            q1 = torch.randn(batch, H, 1, D, device=dev).to(bf)
+            add("decode: Llama attention over its key/value cache",
+                _time(lambda: OF.attention(q1, k, v, causal=False, scale=D ** -0.5), flush=flush), k.numel() * 4)
+        hb = torch.randn(T, n, device=dev).to(bf)
+        add(f"{phase}: router (sigmoid, top-{top} of {E})", _time(lambda: KF.moe_route(hb, moe.router, top, 1.0), flush=flush),
+            T * n * 2 + E * n * 2)
+        if phase == "prefill":
+            add("prefill: experts (sort, per-expert tcgen05 GEMMs, gated activation; one host read of the counts)",
+                _time(lambda: moe(hb), flush=flush), 0.0, T * top * 3 * ff * n * 2.0)
+            add("prefill: Llama gated feed-forward of the active size (tcgen05 GEMMs)", _time(lambda: lmlp(hb), flush=flush), 0.0,
+                T * 3 * top * ff * n * 2.0)
+        else:
+            idx, wts = KF.moe_route(hb, moe.router, top, 1.0)
+            used = int(torch.unique(idx).numel())
+            add("decode: experts, pair by pair (two kernels)",
+                _time(lambda: KF.moe_pairs(hb, moe.gate_up, moe.down, idx, wts, KF.ACT_SILU), flush=flush), used * 3 * ff * n * 2)
+            add("decode: Llama gated feed-forward of the active size", _time(lambda: lmlp(hb), flush=flush), 3 * top * ff * n * 2)
+    return {"peaks": src, "hbm_bytes_per_s": hbm, "bf16_flops": flops, "rows": rows}
+
+
 def main(args):
     assert torch.cuda.is_available(), "the serving bench needs a GPU"
     from libai_b200 import ops
 
     ops.reset_launch_count()
+    if getattr(args, "serving_model", "bumodra") == "nefelorn":
+        result = {"metric": "prefill / decode tokens per second, Nefelorn beside Llama at equal width, depth and active feed-forward size",
+                  "dtype": "bf16", "data": "synthetic tokens, random-init weights", "n_gpus": 1, "sizes": {}}
+        for name in (args.serving_sizes.split(",") if args.serving_sizes else list(NEFELORN_SIZES)):
+            s = NEFELORN_SIZES[name]
+            r = throughput_nefelorn(s, args.serving_batch, args.serving_prompt, new_tokens=max(args.steps, 8),
+                                    steps=max(args.steps // 2, 3), warmup=max(args.warmup, 3))
+            if args.serving_kernels:
+                r["kernels"] = kernel_table_nefelorn(s, args.serving_batch, args.serving_prompt)
+            result["sizes"][name] = {"config": dict(s), "batch": args.serving_batch, "prompt": args.serving_prompt, **r}
+            torch.cuda.empty_cache()
+        result["gpu_launches"] = ops.launch_count()
+        print(json.dumps(result))
+        return
     result = {"metric": "prefill / decode tokens per second, Bumodra beside Llama at equal width, depth and parameter count",
               "dtype": "bf16", "data": "synthetic tokens, random-init weights", "n_gpus": 1, "sizes": {}}
     for name in (args.serving_sizes.split(",") if args.serving_sizes else list(SIZES)):

@@ -302,8 +302,9 @@ def moe_route(h, wr, top: int, rscale: float, counts=None):
     idx = torch.empty(T, top, dtype=torch.int32, device=h.device)
     wts = torch.empty(T, top, dtype=torch.float32, device=h.device)
     if _native(h):
+        z = router_logits(h, wr)
         count_launch()
-        load_kv_ext().moe_route(h, wr, top, float(rscale), idx, wts, counts)
+        load_kv_ext().moe_topk(z, top, float(rscale), idx, wts, counts)
         return idx, wts
     s = torch.sigmoid(F.linear(h.float(), wr.float()))
     tv, ti = s.topk(top, -1)
@@ -312,6 +313,20 @@ def moe_route(h, wr, top: int, rscale: float, counts=None):
     if counts is not None:
         counts.add_(torch.bincount(ti.reshape(-1), minlength=counts.numel()).to(counts.dtype))
     return idx, wts
+
+
+def router_logits(h, wr):
+    """``h @ W_rᵀ`` in fp32: bf16 operands go through the tcgen05 GEMM with its fp32 epilogue (products of bf16 numbers are
+    exact in fp32 and the accumulator is fp32, so nothing is rounded to 16 bits); anything else is an fp32 product."""
+    from . import use_native
+
+    h, wr = h.detach(), wr.detach()
+    if (h.dtype == torch.bfloat16 and wr.dtype == torch.bfloat16 and use_native(h) and h.stride(1) == 1 and h.stride(0) % 8 == 0
+            and h.shape[1] % 8 == 0 and wr.is_contiguous() and wr.shape[0] % 8 == 0 and h.data_ptr() % 16 == 0 and h.shape[0] > 0):
+        z = torch.empty(h.shape[0], wr.shape[0], dtype=torch.float32, device=h.device)
+        if _tcgen05_gemm(h, wr, z, False, torch.float32) is not None:
+            return z
+    return F.linear(h.float(), wr.float())
 
 
 def moe_pairs(h, wgu, wd, idx, wts, act: int):
@@ -339,19 +354,38 @@ def moe_pairs(h, wgu, wd, idx, wts, act: int):
 
 def moe_sorted(h, wgu, wd, idx, counts, act: int):
     """Experts for many tokens: the rows are copied into a matrix sorted by expert, every expert runs as two dense products on
-    its row range (the framework's GEMM), and the caller gathers the weighted sum (:func:`dyt_residual` with ``pos``).  Returns
-    ``(ys fp32 [tokens·top, width], pos int32 [tokens, top])``: the output row of pair (t, k) is ``ys[pos[t, k]]``.  The per-expert
-    row counts are read back by the host (one synchronisation), so this form is for prompt steps, not for captured graphs."""
+    its row range, and the caller gathers the weighted sum (:func:`dyt_residual` with ``pos``).  Returns
+    ``(ys fp32 [rows, width], pos int32 [tokens, top])``: the output row of pair (t, k) is ``ys[pos[t, k]]``.
+
+    bf16 on the GPU: every expert's range starts on a multiple of 128 rows and each product is ONE launch of the tcgen05 GEMM
+    in its grouped mode (the expert of every 128-row block is a device-side list), so nothing is read back by the host and the
+    step can be captured.  Otherwise (fp32, CPU) the per-expert row counts are read back and the experts run one by one."""
     T, n = h.shape
     top, E, ff = idx.shape[1], wgu.shape[0], wgu.shape[1] // 2
     P = T * top
     dev = h.device
-    xs = torch.empty(P, n, dtype=h.dtype, device=dev)
     pos = torch.empty(T, top, dtype=torch.int32, device=dev)
+    if _native(h) and h.dtype == torch.bfloat16 and n % 8 == 0 and ff % 8 == 0 and E * max(2 * ff, n) < 2 ** 31:
+        from . import load_ext
+
+        rows = (P + E * 127 + 127) // 128 * 128
+        xs = torch.empty(rows, n, dtype=h.dtype, device=dev)
+        meta = torch.empty(2 * E + 1 + rows // 128, dtype=torch.int32, device=dev)
+        groups = meta[2 * E + 1:]
+        count_launch(5)
+        load_kv_ext().moe_sort(h, idx, counts, meta[: E + 1], meta[E + 1: 2 * E + 1], pos, xs, 128, groups)
+        gu = torch.empty(rows, 2 * ff, dtype=h.dtype, device=dev)
+        load_ext().gemm_grouped_blocks(xs, wgu.detach(), groups, gu)
+        a = torch.empty(rows, ff, dtype=h.dtype, device=dev)
+        act_rows(gu, a, act, gated=True)
+        ys = torch.empty(rows, n, dtype=torch.float32, device=dev)
+        load_ext().gemm_grouped_blocks(a, wd.detach(), groups, ys)
+        return ys, pos
+    xs = torch.empty(P, n, dtype=h.dtype, device=dev)
     if _native(h):
         count_launch(2)
         meta = torch.empty(2 * E + 1, dtype=torch.int32, device=dev)
-        load_kv_ext().moe_sort(h, idx, counts, meta[: E + 1], meta[E + 1:], pos, xs)
+        load_kv_ext().moe_sort(h, idx, counts, meta[: E + 1], meta[E + 1:], pos, xs, 1, None)
         cnt = counts.tolist()
     else:
         order = torch.sort(idx.reshape(-1).long(), stable=True).indices
@@ -359,17 +393,29 @@ def moe_sorted(h, wgu, wd, idx, counts, act: int):
         xs.copy_(h[order // top])
         cnt = torch.bincount(idx.reshape(-1).long(), minlength=E).tolist()
     gu = torch.empty(P, 2 * ff, dtype=h.dtype, device=dev)
-    at = 0
-    for e, c in enumerate(cnt):
-        if c:
-            linear_into(xs[at:at + c], wgu[e], gu[at:at + c])
-            at += c
     a = torch.empty(P, ff, dtype=h.dtype, device=dev)
-    act_rows(gu, a, act, gated=True)
     ys = torch.empty(P, n, dtype=torch.float32, device=dev)
-    at = 0
-    for e, c in enumerate(cnt):
-        if c:
-            linear_into(a[at:at + c], wd[e], ys[at:at + c])
-            at += c
+    _grouped_products(xs, wgu, cnt, gu, False)
+    act_rows(gu, a, act, gated=True)
+    _grouped_products(a, wd, cnt, ys, False)
     return ys, pos
+
+
+def _grouped_products(a, w, counts, out, grouped: bool):
+    """Rows ``[Σ counts[:e], +counts[e])`` of ``a`` times ``w[e]ᵀ`` into the same rows of ``out``: on the tcgen05 GEMM all
+    groups are launched from one native call; otherwise group by group."""
+    if grouped:
+        from . import load_ext
+
+        try:
+            load_ext().gemm_grouped(a, w.detach(), counts, out)
+            count_launch(sum(1 for c in counts if c))
+            return
+        except RuntimeError as e:
+            if "failed with code -" not in str(e):      # a CUDA error, not a refusal by the launcher's shape checks
+                raise
+    at = 0
+    for e, c in enumerate(counts):
+        if c:
+            linear_into(a[at:at + c], w[e], out[at:at + c])
+            at += c

@@ -466,6 +466,36 @@ def test_tensor_core_prompts_and_grouped_decode_match_the_generic_kernels(tmp_pa
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("T", [17, 300, 1500])
+@torch.no_grad()
+def test_grouped_expert_products_in_bf16(T):
+    """bf16 prompts: experts as two launches of the grouped GEMM over rows sorted by expert (ranges padded to 128 rows, one
+    expert without any token, one with several row blocks) against the pair-by-pair kernels and the float64 oracle."""
+    width, ff, experts, top, scale = 64, 32, 7, 2, 1.3
+    cfg = O.model_cfg([O.chunk_attention_cfg(mlp=O.moe_cfg(ff, experts, top, scale))], width=width)
+    W = O.random_weights(cfg, seed=5)
+    W["l0.mlp.router"][3] = -W["l0.mlp.router"][0] * 4.0 - 1.0      # rarely, if ever, chosen
+    W["l0.mlp.router"][0] = W["l0.mlp.router"][0] * 4.0             # chosen by about half of the tokens
+    with param_defaults(dtype=torch.bfloat16, device="cuda"):
+        moe = MoEFeedForward(width, ff, experts, top, router_scale=scale)
+        ident = DynamicTanh(width)
+    moe.router.copy_(W["l0.mlp.router"])
+    moe.gate_up.copy_(torch.stack([torch.cat([W[f"l0.mlp.e{e}.gate"], W[f"l0.mlp.e{e}.up"]]) for e in range(experts)]))
+    moe.down.copy_(torch.stack([W[f"l0.mlp.e{e}.down"] for e in range(experts)]))
+    ident.alpha.fill_(2.0 ** -10)                                   # tanh(a v) / a ≈ v
+    ident.weight.fill_(2.0 ** 10)
+    h = torch.randn(T, width, generator=torch.Generator().manual_seed(T)).to(torch.bfloat16)
+    pairs, _, _ = moe(h.cuda(), graph_safe=True)
+    ys, pos, cw = moe(h.cuda())
+    assert pos is not None and ys.shape[0] % 128 == 0
+    x = torch.zeros(T, width, device="cuda")
+    KF.dyt_residual(x, ys, post=ident.triple(), pos=pos, cw=cw)
+    assert rel_err(x, pairs.cpu()) < 2e-2                           # both round to bf16, at different places
+    want = torch.stack([O.moe_ff(h[t].double(), W, "l0.", cfg["layers"][0]["mlp"]["router"]) for t in range(min(T, 40))])
+    assert rel_err(x[:40], want) < 2e-2 and rel_err(pairs[:40], want) < 2e-2
+
+
+@pytest.mark.gpu
 def test_serving_precision_and_graphed_steps(tmp_path):
     cfg = mixed_cfg(width=32)
     W = O.random_weights(cfg, seed=3)
