@@ -421,16 +421,16 @@ __device__ __forceinline__ int mask_floor(int p, int window, int chunk) {
 }
 
 template <int D, int V>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 masked_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long ldq, const __nv_bfloat16* __restrict__ kbase,
                             const __nv_bfloat16* __restrict__ vbase, long ldkv, const int* __restrict__ ext_off,
                             const int* __restrict__ nsink, const int* __restrict__ cstart, const __nv_bfloat16* __restrict__ gate, long ldg,
                             const int* __restrict__ qt_seq, const int* __restrict__ qt_start, const int* __restrict__ seq_off,
                             const int* __restrict__ past, __nv_bfloat16* __restrict__ y, long ldy, int H, int G, int window, int chunk,
                             int keep, float scale) {
-  constexpr int KT = 64, KS = D + 8, VS = V + 8;
-  __shared__ __align__(16) __nv_bfloat16 Ks[KT * KS];
-  __shared__ __align__(16) __nv_bfloat16 Vs[KT * VS];
+  constexpr int KT = 64, KS = D + 8, VS = V + 8, BUF = KT * (KS + VS);
+  extern __shared__ __align__(16) unsigned char mma_smem[];              // two buffers of [K tile | V tile]
+  __nv_bfloat16* const tiles = reinterpret_cast<__nv_bfloat16*>(mma_smem);
   const int h = blockIdx.y, g = h / (H / G), b = qt_seq[blockIdx.x], t0 = qt_start[blockIdx.x];
   const int n = seq_off[b + 1] - seq_off[b], p0 = past[b];
   const long elo = ext_off[b];
@@ -459,41 +459,71 @@ masked_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long ldq, const
   const int mrow0 = ns + lo_first - cs, mrow1 = ns + p_last - cs;       // contiguous range, as rows of this sequence
   const int pw0 = p0 + t0 + warp * 16, pw1 = pw0 + 15;                  // positions of this warp's queries
   const int low0 = mask_floor(pw0, window, chunk);
-  const int tilesA = (nA + KT - 1) / KT, tilesB = (mrow1 - mrow0) / KT + 1;
-  for (int it = 0; it < tilesA + tilesB; ++it) {
-    const bool phaseA = it < tilesA;
-    const int k0 = phaseA ? it * KT : mrow0 + (it - tilesA) * KT;       // first row of the tile
-    const int rlim = phaseA ? nA : erows;                                // rows of the tile at or beyond it do not count
-    __syncthreads();
+  const int tilesA = (nA + KT - 1) / KT, tilesB = (mrow1 - mrow0) / KT + 1, ntiles = tilesA + tilesB;
+  // tile `it` goes to buffer it & 1 by cp.async (rows at or beyond the tile's limit are zero-filled: source size 0); the
+  // copy of tile it + 1 is in flight while tile it is multiplied
+  auto prefetch = [&](int it) {
+    const bool pa = it < tilesA;
+    const int k0 = pa ? it * KT : mrow0 + (it - tilesA) * KT, rlim = pa ? nA : erows;
+    __nv_bfloat16* kd = tiles + (it & 1) * BUF;
+    __nv_bfloat16* vd = kd + KT * KS;
     for (int c = threadIdx.x; c < KT * (D / 8); c += 128) {
       const int row = c / (D / 8), ch = c - row * (D / 8);
-      uint4 val = make_uint4(0u, 0u, 0u, 0u);
-      if (k0 + row < rlim) val = *reinterpret_cast<const uint4*>(kbase + (elo + k0 + row) * ldkv + g * D + ch * 8);
-      *reinterpret_cast<uint4*>(&Ks[row * KS + ch * 8]) = val;
+      const bool ok = k0 + row < rlim;
+      const __nv_bfloat16* src = kbase + (elo + (ok ? k0 + row : 0)) * ldkv + g * D + ch * 8;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"((uint32_t)__cvta_generic_to_shared(kd + row * KS + ch * 8)),
+                   "l"(src), "r"(ok ? 16 : 0));
     }
     for (int c = threadIdx.x; c < KT * (V / 8); c += 128) {
       const int row = c / (V / 8), ch = c - row * (V / 8);
-      uint4 val = make_uint4(0u, 0u, 0u, 0u);
-      if (k0 + row < rlim) val = *reinterpret_cast<const uint4*>(vbase + (elo + k0 + row) * ldkv + g * V + ch * 8);
-      *reinterpret_cast<uint4*>(&Vs[row * VS + ch * 8]) = val;
+      const bool ok = k0 + row < rlim;
+      const __nv_bfloat16* src = vbase + (elo + (ok ? k0 + row : 0)) * ldkv + g * V + ch * 8;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"((uint32_t)__cvta_generic_to_shared(vd + row * VS + ch * 8)),
+                   "l"(src), "r"(ok ? 16 : 0));
     }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  prefetch(0);
+  for (int it = 0; it < ntiles; ++it) {
+    const bool phaseA = it < tilesA;
+    const int k0 = phaseA ? it * KT : mrow0 + (it - tilesA) * KT;       // first row of the tile
+    const int rlim = phaseA ? nA : erows;                                // rows of the tile at or beyond it do not count
+    if (it + 1 < ntiles) {
+      prefetch(it + 1);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    }
+    __syncthreads();                                                      // every thread's part of tile `it` has landed
+    const __nv_bfloat16* Ks = tiles + (it & 1) * BUF;
+    const __nv_bfloat16* Vs = Ks + KT * KS;
+    bool skip = false;
     if (!phaseA) {                                                        // nothing in this tile for the warp's 16 queries?
       const int kp0 = cs + k0 - ns, kp1 = kp0 + KT - 1;                  // positions of the tile's first and last row
-      if (kp0 > pw1 || (kp1 < low0 && kp0 >= keep)) continue;
+      skip = kp0 > pw1 || (kp1 < low0 && kp0 >= keep);
     }
+    if (!skip) {
     float sacc[8][4];
 #pragma unroll
     for (int j = 0; j < 8; ++j) { sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f; }
+    // B fragments of two key blocks (j, j + 1) per ldmatrix.x4: lanes 0-7 / 8-15 address the rows of block j at channels
+    // kk*16 / kk*16 + 8, lanes 16-23 / 24-31 the same of block j + 1
+    const uint32_t krow = (uint32_t)__cvta_generic_to_shared(&Ks[((lane >> 4) * 8 + (lane & 7)) * KS + ((lane >> 3) & 1) * 8]);
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const __nv_bfloat16* kr = &Ks[(j * 8 + gid) * KS + kk * 16 + tig * 2];
-        mma_bf16(sacc[j], qf[kk], *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 8));
+      for (int j = 0; j < 8; j += 2) {
+        uint32_t b0, b1, b2, b3;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                     : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(krow + (j * 8 * KS + kk * 16) * 2));
+        mma_bf16(sacc[j], qf[kk], b0, b1);
+        mma_bf16(sacc[j + 1], qf[kk], b2, b3);
       }
     }
     float mx0 = -INFINITY, mx1 = -INFINITY;
+    // a tile that every query of the warp sees completely needs no mask
+    const bool whole = phaseA ? (k0 + KT <= rlim)
+                              : (k0 + KT <= rlim && cs + k0 - ns + KT - 1 <= pw0 && cs + k0 - ns >= mask_floor(pw1, window, chunk));
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
 #pragma unroll
@@ -501,7 +531,7 @@ masked_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long ldq, const
         const int row = k0 + j * 8 + tig * 2 + (c & 1);
         const int pj = row < ns ? row : cs + row - ns;
         const int pi = c < 2 ? pi0 : pi1, lo = c < 2 ? lo0 : lo1;
-        const bool valid = row < rlim && pj <= pi && (phaseA || pj >= lo || pj < keep);
+        const bool valid = whole || (row < rlim && pj <= pi && (phaseA || pj >= lo || pj < keep));
         const float sv = valid ? sacc[j][c] * scale : -INFINITY;
         sacc[j][c] = sv;
         if (c < 2) mx0 = fmaxf(mx0, sv); else mx1 = fmaxf(mx1, sv);
@@ -538,6 +568,8 @@ masked_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long ldq, const
         mma_bf16(o[j], a, b0, b1);
       }
     }
+      }                                                                   // (!skip)
+    __syncthreads();                                                      // all warps are done with this buffer before tile it + 2 overwrites it
   }
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
@@ -1001,9 +1033,13 @@ int lbk_masked_attention_mma(const void* q, long ldq, const void* kbase, const v
   if (n_qtiles == 0) return 0;
   if (D != V || G <= 0 || H % G) return -1;
   const dim3 grid((unsigned)n_qtiles, (unsigned)H);
-#define MMA_CASE(DD) case DD: masked_attention_mma_kernel<DD, DD><<<grid, 128, 0, s>>>((const bf16*)q, ldq, (const bf16*)kbase, \
+#define MMA_CASE(DD) case DD: { \
+    constexpr int smem = 2 * 64 * (2 * DD + 16) * 2; \
+    static bool once = false; \
+    if (!once) { cudaFuncSetAttribute(masked_attention_mma_kernel<DD, DD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); once = true; } \
+    masked_attention_mma_kernel<DD, DD><<<grid, 128, smem, s>>>((const bf16*)q, ldq, (const bf16*)kbase, \
     (const bf16*)vbase, ldkv, ext_off, nsink, cstart, (const bf16*)gate, ldg, qt_seq, qt_start, seq_off, past, (bf16*)y, ldy, H, G, \
-    window, chunk, keep, scale); break
+    window, chunk, keep, scale); } break
   switch (D) {
     MMA_CASE(32); MMA_CASE(48); MMA_CASE(64); MMA_CASE(96); MMA_CASE(128);
     default: return -1;
