@@ -521,20 +521,32 @@ masked_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long ldq, const
       }
     }
     float mx0 = -INFINITY, mx1 = -INFINITY;
-    // a tile that every query of the warp sees completely needs no mask
+    // a tile that every query of the warp sees completely needs no mask (warp-uniform)
     const bool whole = phaseA ? (k0 + KT <= rlim)
                               : (k0 + KT <= rlim && cs + k0 - ns + KT - 1 <= pw0 && cs + k0 - ns >= mask_floor(pw1, window, chunk));
+    if (whole) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 8; ++j) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int row = k0 + j * 8 + tig * 2 + (c & 1);
-        const int pj = row < ns ? row : cs + row - ns;
-        const int pi = c < 2 ? pi0 : pi1, lo = c < 2 ? lo0 : lo1;
-        const bool valid = whole || (row < rlim && pj <= pi && (phaseA || pj >= lo || pj < keep));
-        const float sv = valid ? sacc[j][c] * scale : -INFINITY;
-        sacc[j][c] = sv;
-        if (c < 2) mx0 = fmaxf(mx0, sv); else mx1 = fmaxf(mx1, sv);
+        for (int c = 0; c < 4; ++c) {
+          const float sv = sacc[j][c] * scale;
+          sacc[j][c] = sv;
+          if (c < 2) mx0 = fmaxf(mx0, sv); else mx1 = fmaxf(mx1, sv);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int row = k0 + j * 8 + tig * 2 + (c & 1);
+          const int pj = row < ns ? row : cs + row - ns;
+          const int pi = c < 2 ? pi0 : pi1, lo = c < 2 ? lo0 : lo1;
+          const bool valid = row < rlim && pj <= pi && (phaseA || pj >= lo || pj < keep);
+          const float sv = valid ? sacc[j][c] * scale : -INFINITY;
+          sacc[j][c] = sv;
+          if (c < 2) mx0 = fmaxf(mx0, sv); else mx1 = fmaxf(mx1, sv);
+        }
       }
     }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
@@ -553,19 +565,25 @@ masked_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long ldq, const
       }
     }
     l0 = l0 * c0 + s0; l1 = l1 * c1 + s1; m0 = mn0; m1 = mn1;
+    if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {              // a row maximum moved: rescale (multiplying by 1 is exact, so skipping is too)
 #pragma unroll
-    for (int j = 0; j < V / 8; ++j) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+      for (int j = 0; j < V / 8; ++j) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+    }
 #pragma unroll
     for (int k2 = 0; k2 < 4; ++k2) {
       uint32_t a[4];
       a[0] = pack_bf16(sacc[2 * k2][0], sacc[2 * k2][1]); a[1] = pack_bf16(sacc[2 * k2][2], sacc[2 * k2][3]);
       a[2] = pack_bf16(sacc[2 * k2 + 1][0], sacc[2 * k2 + 1][1]); a[3] = pack_bf16(sacc[2 * k2 + 1][2], sacc[2 * k2 + 1][3]);
-      const uint32_t vrow = (uint32_t)__cvta_generic_to_shared(&Vs[(k2 * 16 + (lane & 15)) * VS]);
+      // V fragments of two channel blocks (j, j + 1) per ldmatrix.x4.trans: lanes 0-15 address the 16 key rows at channels
+      // j*8, lanes 16-31 the same rows at channels (j + 1)*8
+      const uint32_t vrow = (uint32_t)__cvta_generic_to_shared(&Vs[(k2 * 16 + (lane & 15)) * VS + (lane >> 4) * 8]);
 #pragma unroll
-      for (int j = 0; j < V / 8; ++j) {
-        uint32_t b0, b1;
-        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(b0), "=r"(b1) : "r"(vrow + j * 16));
+      for (int j = 0; j < V / 8; j += 2) {
+        uint32_t b0, b1, b2, b3;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                     : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(vrow + j * 16));
         mma_bf16(o[j], a, b0, b1);
+        mma_bf16(o[j + 1], a, b2, b3);
       }
     }
       }                                                                   // (!skip)

@@ -367,7 +367,7 @@ def kernel_table_nefelorn(s, batch, prompt):
         add(f"{phase}: router (sigmoid, top-{top} of {E})", _time(lambda: KF.moe_route(hb, moe.router, top, 1.0), flush=flush),
             T * n * 2 + E * n * 2)
         if phase == "prefill":
-            add("prefill: experts (sort, per-expert tcgen05 GEMMs, gated activation; one host read of the counts)",
+            add("prefill: experts (sort by expert, two grouped tcgen05 GEMM launches, gated activation)",
                 _time(lambda: moe(hb), flush=flush), 0.0, T * top * 3 * ff * n * 2.0)
             add("prefill: Llama gated feed-forward of the active size (tcgen05 GEMMs)", _time(lambda: lmlp(hb), flush=flush), 0.0,
                 T * 3 * top * ff * n * 2.0)
