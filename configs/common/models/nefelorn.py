@@ -11,7 +11,7 @@ def _moe(ff, experts=8, top=2):
 
 def _chunked(kv_from=None, mlp=None):
     m = dict(heads=8, kv_heads=2, dim=64, vdim=64, mask=dict(size=256), scale=0.125,
-             rot=dict(dims=64, base=500000.0, scaling=dict(factor=8.0, original=2048, fast=32.0, slow=1.0)))
+             rot=dict(dims=64, base=500000.0, scaling=dict(factor=4.0, original=4096, fast=24.0, slow=2.0)))
     if kv_from is not None:
         m["kv_from"] = kv_from
     return dict(type="attention", mixer=m, mlp=mlp)
@@ -19,13 +19,13 @@ def _chunked(kv_from=None, mlp=None):
 
 def _windowed(mlp=None):
     return dict(type="attention_2", mlp=mlp,
-                mixer=dict(heads=8, kv_heads=2, dim=64, vdim=64, mask=dict(size=512, keep_first=4), scale=0.125,
+                mixer=dict(heads=8, kv_heads=2, dim=64, vdim=64, mask=dict(size=512, keep_first=8), scale=0.125,
                            rot=dict(dims=32, base=10000.0)))
 
 
 cfg = DictConfig(
     dict(
-        vocab=32000, width=512, norm=dict(eps=1e-6), embedding=dict(scale=22.6), logit_softcap=30.0,
+        vocab=32000, width=512, norm=dict(eps=1e-6), embedding=dict(scale=22.6), logit_softcap=50.0,
         layers=[_chunked(mlp=dict(kind="dense", ff=2048)), _windowed(mlp=_moe(512)), _chunked(kv_from=0, mlp=_moe(512)),
                 _windowed(mlp=_moe(512))],
         initializer_range=0.02,

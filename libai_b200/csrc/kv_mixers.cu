@@ -130,6 +130,58 @@ __global__ void dyt_residual_kernel(float* __restrict__ x, const Ty* __restrict_
   }
 }
 
+// four consecutive channels per thread (n a multiple of 4, rows 16-byte aligned): 16-byte fp32 and 8-byte bf16 accesses
+template <typename T> __device__ __forceinline__ float4 ld4(const T* p);
+template <> __device__ __forceinline__ float4 ld4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 ld4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename T> __device__ __forceinline__ void st4(T* p, float4 v);
+template <> __device__ __forceinline__ void st4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void st4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename T, typename Ty>
+__global__ void dyt_residual_vec4_kernel(float* __restrict__ x, const Ty* __restrict__ y, long ldy, const int* __restrict__ pos,
+                                         const float* __restrict__ cw, int top, const T* __restrict__ pw, const T* __restrict__ pb,
+                                         const T* __restrict__ palpha, const T* __restrict__ nw, const T* __restrict__ nb,
+                                         const T* __restrict__ nalpha, T* __restrict__ h, long ldh, int n) {
+  const long r = blockIdx.x;
+  const float pa = y ? ldf(palpha) : 0.f, na = h ? ldf(nalpha) : 0.f;
+  for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+    float4 v = *reinterpret_cast<const float4*>(x + r * n + i);
+    if (y) {
+      float4 yv;
+      if (pos) {
+        yv = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < top; ++k) {
+          const float w = cw[r * top + k];
+          const float4 t = ld4<Ty>(y + (long)pos[r * top + k] * ldy + i);
+          yv.x += w * t.x; yv.y += w * t.y; yv.z += w * t.z; yv.w += w * t.w;
+        }
+      } else {
+        yv = ld4<Ty>(y + r * ldy + i);
+      }
+      const float4 w = ld4<T>(pw + i), b = ld4<T>(pb + i);
+      v.x += tanhf(pa * yv.x) * w.x + b.x; v.y += tanhf(pa * yv.y) * w.y + b.y;
+      v.z += tanhf(pa * yv.z) * w.z + b.z; v.w += tanhf(pa * yv.w) * w.w + b.w;
+      *reinterpret_cast<float4*>(x + r * n + i) = v;
+    }
+    if (h) {
+      const float4 w = ld4<T>(nw + i), b = ld4<T>(nb + i);
+      st4<T>(h + r * ldh + i, make_float4(tanhf(na * v.x) * w.x + b.x, tanhf(na * v.y) * w.y + b.y, tanhf(na * v.z) * w.z + b.z,
+                                          tanhf(na * v.w) * w.w + b.w));
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------------------------
 // Elementwise activations between column slices: out = act(in), or — gated — out = act(in[:, :n]) * in[:, n:2n].
 // ------------------------------------------------------------------------------------------------------------------
@@ -214,12 +266,22 @@ qk_prepare_kernel(T* __restrict__ q, long ldq, T* __restrict__ k, long ldk, cons
   T* kr = k ? k + tok * ldk : nullptr;
   float rq = 1.f, rk = 1.f;
   if (full_norm) {
+    // sums of squares over the whole projections; four channels per load where the rows allow it
+    const bool v4 = (D & 3) == 0 && (ldq & 3) == 0 && (ldk & 3) == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)k & 15) == 0;
     float s = 0.f;
-    for (int i = threadIdx.x; i < H * D; i += blockDim.x) { const float v = ldf(qr + i); s += v * v; }
+    if (v4) {
+      for (int i = threadIdx.x * 4; i < H * D; i += blockDim.x * 4) { const float4 v = ld4<T>(qr + i); s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+    } else {
+      for (int i = threadIdx.x; i < H * D; i += blockDim.x) { const float v = ldf(qr + i); s += v * v; }
+    }
     rq = 1.f / sqrtf(block_sum(s, red) / (float)(H * D) + eps);
     if (kr) {
       s = 0.f;
-      for (int i = threadIdx.x; i < G * D; i += blockDim.x) { const float v = ldf(kr + i); s += v * v; }
+      if (v4) {
+        for (int i = threadIdx.x * 4; i < G * D; i += blockDim.x * 4) { const float4 v = ld4<T>(kr + i); s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+      } else {
+        for (int i = threadIdx.x; i < G * D; i += blockDim.x) { const float v = ldf(kr + i); s += v * v; }
+      }
       rk = 1.f / sqrtf(block_sum(s, red) / (float)(G * D) + eps);
     }
   }
@@ -892,7 +954,13 @@ __global__ void moe_scatter_kernel(const T* __restrict__ h, long ldh, const int*
   __syncthreads();
   const T* src = h + (pair / top) * ldh;
   T* dst = xs + (long)where * n;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+  constexpr int PER = 16 / sizeof(T);
+  if (n % PER == 0 && ldh % PER == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)xs & 15) == 0) {
+    for (int i = threadIdx.x; i < n / PER; i += blockDim.x)
+      reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+  }
 }
 
 }  // namespace
@@ -916,7 +984,19 @@ int lbk_dyt_residual(float* x, const void* y, long ldy, int ydtype, const int* p
                      const void* pb, const void* palpha, const void* nw, const void* nb, const void* nalpha, void* h, long ldh,
                      long rows, int n, int dtype, cudaStream_t s) {
   if (rows == 0) return 0;
-  const int th = n >= 1024 ? 256 : 128;
+  int th = n >= 1024 ? 256 : 128;
+  auto al = [](const void* p, int a) { return p == nullptr || ((uintptr_t)p & (a - 1)) == 0; };
+  const bool vec = n % 4 == 0 && ldy % 4 == 0 && ldh % 4 == 0 && al(x, 16) && al(y, 16) && al(h, 16) && al(pw, 16) && al(pb, 16) &&
+                   al(nw, 16) && al(nb, 16);
+  if (vec) {
+    th = n >= 2048 ? 256 : (n >= 512 ? 128 : 64);
+#define DYTV(T, Ty) dyt_residual_vec4_kernel<T, Ty><<<(unsigned)rows, th, 0, s>>>(x, (const Ty*)y, ldy, pos, cw, top, (const T*)pw, \
+    (const T*)pb, (const T*)palpha, (const T*)nw, (const T*)nb, (const T*)nalpha, (T*)h, ldh, n)
+    if (dtype) { if (ydtype) DYTV(bf16, bf16); else DYTV(bf16, float); }
+    else { if (ydtype) return -1; DYTV(float, float); }
+#undef DYTV
+    LAUNCH_END();
+  }
 #define DYT(T, Ty) dyt_residual_kernel<T, Ty><<<(unsigned)rows, th, 0, s>>>(x, (const Ty*)y, ldy, pos, cw, top, (const T*)pw, \
     (const T*)pb, (const T*)palpha, (const T*)nw, (const T*)nb, (const T*)nalpha, (T*)h, ldh, n)
   if (dtype) { if (ydtype) DYT(bf16, bf16); else DYT(bf16, float); }

@@ -198,9 +198,9 @@ def kernel_table(s, batch, prompt):
 # ======================================================================================================================
 NEFELORN_SIZES = {
     # heads × dim with grouped keys, mask reach, experts (top of them active; top · expert_ff = Llama's intermediate size)
-    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, reach=512, keep=4, ff=4096, experts=16, top=2, expert_ff=1408,
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, reach=512, keep=8, ff=4096, experts=16, top=2, expert_ff=1408,
                   blocks=4, vocab=32000),
-    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, reach=1024, keep=4, ff=8192, experts=32, top=2, expert_ff=2816,
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, reach=1024, keep=8, ff=8192, experts=32, top=2, expert_ff=2816,
                   blocks=4, vocab=32000),
 }
 
@@ -211,7 +211,7 @@ def nefelorn_config(s):
 
     def chunked(mlp, kv_from=None):
         m = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": D, "vdim": D, "mask": {"size": s["reach"]}, "scale": D ** -0.5,
-             "rot": {"dims": D, "base": 500000.0, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+             "rot": {"dims": D, "base": 500000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 24.0, "slow": 2.0}}}
         if kv_from is not None:
             m["kv_from"] = kv_from
         return {"type": "attention", "mixer": m, "mlp": mlp}
@@ -228,7 +228,7 @@ def nefelorn_config(s):
         if "kv_from" in lc["mixer"]:
             lc["mixer"]["kv_from"] = i - 2
         layers.append(lc)
-    return dict(vocab=s["vocab"], width=s["width"], norm={"eps": 1e-6}, embedding={"scale": s["width"] ** 0.5}, logit_softcap=30.0,
+    return dict(vocab=s["vocab"], width=s["width"], norm={"eps": 1e-6}, embedding={"scale": s["width"] ** 0.5}, logit_softcap=50.0,
                 layers=layers)
 
 
@@ -313,7 +313,7 @@ def kernel_table_nefelorn(s, batch, prompt):
         na, nb = DynamicTanh(n), DynamicTanh(n)
         moe = MoEFeedForward(n, ff, E, top)
         lmlp = LlamaMLP(n, top * ff)
-    freq, ms_ = KF.rotary_frequencies(D, 5e5, {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0})
+    freq, ms_ = KF.rotary_frequencies(D, 5e5, {"factor": 4.0, "original": 4096, "fast": 24.0, "slow": 2.0})
     freq = freq.to(dev)
     for phase, lens, past in (("prefill", [prompt] * batch, [0] * batch), ("decode", [1] * batch, [prompt] * batch)):
         rb = RaggedBatch(lens, list(range(batch)), past, dev)

@@ -53,6 +53,11 @@ def linear_into(a, w, out):
             return out
     if out.dtype == a.dtype:
         return torch.mm(a, w.t(), out=out) if out.is_contiguous() else out.copy_(F.linear(a, w))
+    if a.is_cuda and a.dtype == torch.bfloat16:
+        try:                                                    # vendor product with an fp32 result: nothing is rounded to bf16
+            return out.copy_(torch.mm(a, w.t(), out_dtype=torch.float32))
+        except (TypeError, RuntimeError):
+            pass
     return out.copy_(F.linear(a, w))
 
 
