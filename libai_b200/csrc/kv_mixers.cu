@@ -195,8 +195,7 @@ __device__ __forceinline__ float act_apply(float v, int act) {
   }
 }
 template <typename T>
-__global__ void act_rows_kernel(const T* __restrict__ in, long ldi, T* __restrict__ out, long ldo, long rows, int n, int act,
-                                int gated) {
+__global__ void act_rows_kernel(const T* in, long ldi, T* out, long ldo, long rows, int n, int act, int gated) {   // in == out is allowed
   const long total = rows * n;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
     const long r = i / n; const int c = (int)(i - r * n);
@@ -207,8 +206,8 @@ __global__ void act_rows_kernel(const T* __restrict__ in, long ldi, T* __restric
 }
 
 // bf16, 8 channels per thread with 16-byte accesses (n a multiple of 8, rows 16-byte aligned)
-__global__ void act_rows_vec8_kernel(const __nv_bfloat16* __restrict__ in, long ldi, __nv_bfloat16* __restrict__ out, long ldo, long rows,
-                                     int n, int act, int gated) {
+__global__ void act_rows_vec8_kernel(const __nv_bfloat16* in, long ldi, __nv_bfloat16* out, long ldo, long rows, int n, int act,
+                                     int gated) {
   const int per = n / 8;
   const long total = rows * per;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
