@@ -334,16 +334,25 @@ def test_one_key_stands_out_at_every_edge(device, tmp_path):
         layer["mixer"]["rot"] = {"dims": 0, "base": 1.0}
         cfg = O.model_cfg([layer], vocab=12, width=8, softcap=None)
         W = O.random_weights(cfg, seed=11)
+        W["l0.mix.k"] = W["l0.mix.q"].clone()                     # one head, no rotation: a token's key is its own query, so the
+        if kind == "chunk":                                       # probe (the same token as the last one) gets the top score
+            W["l0.mix.k.norm"] = W["l0.mix.q.norm"].clone()
         model, _ = make(tmp_path, cfg, device, weights=W)
         n = 37
-        for probe_at in ([0, 1, 2, 3, n - 10, n - 9, n - 8] if kind == "window" else [n - 1 - (n - 1) % 8 - 1, n - 1 - (n - 1) % 8, 7, 8]):
+        # (just inside, just outside) pairs of probe positions: the kept-first rows, the window's far edge, the chunk's start
+        pairs = [(1, 2), (n - 9, n - 10)] if kind == "window" else [(n - 1 - (n - 1) % 8, n - 1 - (n - 1) % 8 - 1), (32, 31)]
+        last = {}
+        for probe_at in sorted({p for pair in pairs for p in pair} | {0, 3, n - 8, 7, 8}):
             toks = [5] * n
             toks[probe_at] = 3
             toks[-1] = 3                                          # the last query looks for the probe's key
             want, _ = O.forward(cfg, W, toks)
+            last[probe_at] = want[-1:]
             for cuts in ([n], [n - 1, 1], [n - 12] + [1] * 12):
                 got, = run_schedule(model, [toks], [cuts])
                 assert rel_err(got[-1:], want[-1:]) < 2e-4, (kind, probe_at, cuts)
+        for inside, outside in pairs:                             # the probe matters: seeing it or not moves the last logits
+            assert rel_err(last[inside], last[outside]) > 100 * 2e-4, (kind, inside, outside)
 
 
 @pytest.mark.parametrize("device", DEVICES)
@@ -359,7 +368,8 @@ def test_long_decoding_over_many_ring_wraps(device, tmp_path):
 
 
 @pytest.mark.parametrize("device", DEVICES)
-@pytest.mark.parametrize("case", ["one_head", "window_one", "keep_beyond_window", "chunk_one", "wide_values", "no_rotation_left"])
+@pytest.mark.parametrize("case", ["one_head", "window_one", "keep_beyond_window", "chunk_one", "two_readers", "wide_values",
+                                  "no_rotation_left"])
 def test_other_sizes(device, tmp_path, case):
     layers = {
         "one_head": [O.chunk_attention_cfg(heads=1, kv_heads=1, dim=16, vdim=2, chunk=4, mlp=O.moe_cfg(ff=3, experts=2, top=2))],
@@ -368,6 +378,11 @@ def test_other_sizes(device, tmp_path, case):
         "chunk_one": [O.chunk_attention_cfg(heads=2, kv_heads=1, dim=4, vdim=4, chunk=1, rot=O.rot_cfg(2, 7.0)),
                       O.chunk_attention_cfg(heads=2, kv_heads=1, dim=4, vdim=4, chunk=3, rot=O.rot_cfg(2, 7.0), kv_from=0,
                                             mlp=O.dense_cfg(8))],
+        "two_readers": [O.chunk_attention_cfg(heads=2, kv_heads=2, dim=4, vdim=6, chunk=4, rot=O.rot_cfg(4, 9.0), mlp=O.moe_cfg(ff=4, experts=4, top=3)),
+                        O.window_attention_cfg(heads=2, kv_heads=1, dim=4, vdim=4, window=3, keep_first=1, rot=O.rot_cfg(4, 9.0)),
+                        O.chunk_attention_cfg(heads=4, kv_heads=2, dim=4, vdim=6, chunk=4, rot=O.rot_cfg(4, 9.0), kv_from=0),
+                        O.chunk_attention_cfg(heads=2, kv_heads=2, dim=4, vdim=6, chunk=9, rot=O.rot_cfg(4, 9.0), kv_from=0,
+                                              mlp=O.dense_cfg(8))],
         "wide_values": [O.window_attention_cfg(heads=2, kv_heads=1, dim=6, vdim=40, window=4, keep_first=1, rot=O.rot_cfg(6, 20.0))],
         "no_rotation_left": [O.window_attention_cfg(heads=2, kv_heads=1, dim=12, vdim=4, window=5, keep_first=0, rot=O.rot_cfg(2, 5.0))],
     }[case]
