@@ -59,6 +59,7 @@ template <>
 __device__ __forceinline__ float warp_dot<float>(const float* __restrict__ w, const float* __restrict__ xs, int n, int lane) {
   float acc = 0.f;
   if ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+#pragma unroll 4
     for (int i = lane * 4; i < n; i += 128) {
       const float4 v = *reinterpret_cast<const float4*>(w + i);
       acc += v.x * xs[i] + v.y * xs[i + 1] + v.z * xs[i + 2] + v.w * xs[i + 3];
@@ -73,6 +74,7 @@ __device__ __forceinline__ float warp_dot<__nv_bfloat16>(const __nv_bfloat16* __
                                                          int lane) {
   float acc = 0.f;
   if ((n & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+#pragma unroll 4
     for (int i = lane * 8; i < n; i += 256) {
       const uint4 raw = *reinterpret_cast<const uint4*>(w + i);
       const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
